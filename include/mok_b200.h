@@ -1,0 +1,205 @@
+/*
+ * C ABI of the B200 (sm_100a) expert-parallel MoE layer library, libmok_b200.so.
+ *
+ * Every entry point takes raw device pointers, sizes and a CUDA stream, enqueues work on that
+ * stream and returns immediately: 0 on success, a negative MOK_ERR_* code when an argument is
+ * rejected or a launch fails.  Nothing here allocates device memory, synchronises with the host
+ * or throws.  Device-side problems (schedule overflow, a wait that ran out) are reported through
+ * the caller-provided `status` word (MOK_STATUS_* bits), which the host may read whenever it likes.
+ *
+ * Each function names the interface of the reference project it stands in for (paths are inside
+ * that project).  Peer pointer arrays hold one device virtual address per expert-parallel rank,
+ * as `torch.distributed._symmetric_memory` hands them out (mok/functional.py:211-225).
+ */
+#ifndef MOK_B200_H
+#define MOK_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct CUstream_st* mok_stream_t;
+
+enum {
+    MOK_OK = 0,
+    MOK_ERR_INVALID_ARGUMENT = -1,
+    MOK_ERR_UNSUPPORTED = -2,
+    MOK_ERR_CUDA = -3,
+    MOK_ERR_TOO_LARGE = -4
+};
+
+/* bits of the device status word */
+enum {
+    MOK_STATUS_SCHEDULE_OVERFLOW = 1u,   /* padded routes exceed schedule_capacity; rows beyond it were dropped */
+    MOK_STATUS_BARRIER_TIMEOUT = 2u,     /* a cross-GPU barrier wait ran out */
+    MOK_STATUS_PIPELINE_TIMEOUT = 4u,    /* an mbarrier wait inside a GEMM kernel ran out */
+    MOK_STATUS_BAD_SCHEDULE_ENTRY = 8u   /* a schedule row named a peer or token outside the buffers (skipped) */
+};
+
+#define MOK_MAX_EP 8
+#define MOK_MAX_LOCAL_EXPERTS 1024
+
+/* Library/ABI version (major*100+minor); also proves the library loaded. */
+int mok_version(void);
+
+/* Last CUDA error string seen by this library on the calling thread ("" if none). */
+const char* mok_last_error(void);
+
+/* Bytes of int32 scratch `mok_schedule` needs for these sizes. */
+int64_t mok_schedule_scratch_bytes(int ep_size, int num_local_tokens, int topk, int num_local_experts);
+
+/*
+ * Builds this rank's padded per-expert receive schedule from the all-gathered routes.
+ * Replaces: scheduler::schedule_entrypoint, csrc/scheduler.cuh:149-183 (count/pad/schedule kernels :35-147);
+ * op `mok::schedule`, mok/ops.py:109-156.  Ordering contract: csrc/scheduler.cuh:134-139.
+ *   topk_all            int32 [ep, T, K]
+ *   peer_rank           int32 [cap]   (-1 on padding rows)
+ *   peer_token_idx      int32 [cap]   (token*K + k on the source rank; -1 on padding rows)
+ *   num_tokens          int32 [1]     padded total
+ *   tokens_per_expert   int32 [E_loc] each padded to 256
+ *   scratch             mok_schedule_scratch_bytes() bytes
+ *   status              uint32 [1], OR-ed with MOK_STATUS_SCHEDULE_OVERFLOW instead of trapping (csrc/scheduler.cuh:86)
+ */
+int mok_schedule(const int32_t* topk_all, int ep_size, int num_local_tokens, int topk,
+                 int num_local_experts, int schedule_capacity, int rank,
+                 int32_t* peer_rank, int32_t* peer_token_idx, int32_t* num_tokens,
+                 int32_t* tokens_per_expert, int32_t* scratch, uint32_t* status, mok_stream_t stream);
+
+/*
+ * Copies this rank's int32 routes [T*K] into slot `rank` of the [ep, T, K] buffer of every peer.
+ * Replaces: all_gather_top_experts_kernel, csrc/utils.cuh:191-227 (op mok/ops.py:6-61).  Peers are
+ * addressed one by one through `peer_buffers` (unicast stores); no multicast object is needed.
+ */
+int mok_all_gather_top_experts(const int32_t* top_experts, int64_t num_routes, const uint64_t* peer_buffers,
+                               int ep_size, int rank, mok_stream_t stream);
+
+/*
+ * Device-side barrier across the EP ranks.  Replaces: barrier_all_kernel, csrc/utils.cuh:229-299
+ * (op mok/ops.py:64-106).  `target` (int32 [1], local) is advanced by ep_size, every peer's counter
+ * receives +1 with release/system semantics, then the local counter is polled until it reaches the
+ * target.  The poll is bounded (`timeout_ms`, 0 = default 20 s): on expiry MOK_STATUS_BARRIER_TIMEOUT is
+ * set and the kernel returns.
+ */
+int mok_barrier_all(int32_t* local_counter, const uint64_t* peer_counters, int ep_size, int32_t* target,
+                    uint32_t* status, int timeout_ms, mok_stream_t stream);
+
+/*
+ * out[t] = bf16(y_shared[t] + sum_k w[t,k] * combine[t*K+k]) with k ascending in fp32.
+ * Replaces: fwd_epilogue_kernel, csrc/utils.cuh:43-95 (op mok/ops.py:1279-1313).  y_shared may be NULL (treated as 0).
+ */
+int mok_fwd_epilogue(const void* y_shared, const void* combine_buffer, const float* topk_weights, void* out,
+                     int64_t num_local_tokens, int hidden, int topk, mok_stream_t stream);
+
+/*
+ * d_x[t] = bf16(d_x_shared[t] + sum_k d_x_routed[t*K+k]).  Replaces: bwd_epilogue_kernel,
+ * csrc/utils.cuh:140-176 (op mok/ops.py:1316-1349).  d_x_shared may be NULL.
+ */
+int mok_bwd_epilogue(const void* d_x_shared, const void* d_x_routed_buffer, void* out,
+                     int64_t num_local_tokens, int hidden, int topk, mok_stream_t stream);
+
+/*
+ * bf16 [E, M, N] -> e4m3 + e8m0 scale per 32 elements along the row, optionally also of the transpose.
+ * Replaces: mxfp8::quantize_kernel, csrc/mxfp8.cuh:188-280 (op mok/ops.py:159-197).  Scale bytes go to the
+ * [rows/128, cols/128, 32, 16] tensor-core layout (csrc/mxfp8.cuh:181-184).  Any of the four outputs may be
+ * NULL in pairs (fp8, sc) / (fp8_t, sc_t).
+ */
+int mok_mxfp8_quantize(const void* x_bf16, int num_matrices, int rows, int cols,
+                       void* x_fp8, void* x_sc, void* x_fp8_t, void* x_sc_t, mok_stream_t stream);
+
+/* Arguments shared by the fused-layer entry points below.  All tensor pointers are device pointers;
+ * bf16 unless stated.  Pointers not needed by a call may be NULL where noted. */
+typedef struct mok_layer_args {
+    /* sizes */
+    int ep_size, rank;
+    int num_local_tokens;      /* T */
+    int hidden;                /* H */
+    int intermediate;          /* I */
+    int num_local_experts;     /* E_loc */
+    int topk;                  /* K */
+    int schedule_capacity;     /* rows of the schedule arrays */
+    int macrobatch_size;       /* rows of the routed activation buffers */
+    int minibatch_size;
+    int num_comm_sms;
+    int has_swiglu_limit;
+    float swiglu_limit;
+    int reserved0;
+    /* schedule (mok_schedule outputs) */
+    const int32_t* peer_rank;
+    const int32_t* peer_token_idx;
+    const int32_t* num_tokens;
+    const int32_t* tokens_per_expert;
+    /* this rank's own token-major inputs (what x_ptrs[rank] / d_y_ptrs[rank] point at) */
+    const void* x_local;                  /* [T, H] */
+    const void* d_y_local;                /* [T, H] (backward) */
+    /* symmetric buffers: one address per rank */
+    const uint64_t* x_ptrs;               /* [T, H] */
+    const uint64_t* combine_ptrs;         /* [T*K, H] (forward) */
+    const uint64_t* d_y_ptrs;             /* [T, H] (backward) */
+    const uint64_t* d_x_routed_ptrs;      /* [T*K, H] (backward) */
+    const uint64_t* router_weight_ptrs;   /* fp32 [T, K] (backward) */
+    const uint64_t* d_router_weight_ptrs; /* fp32 [T, K] (backward) */
+    /* weights; shared ones may be NULL = no shared expert */
+    const void *w_shared_gate, *w_shared_up, *w_shared_down;   /* [I,H] [I,H] [H,I] */
+    const void *w_routed_gate, *w_routed_up, *w_routed_down;   /* [E,I,H] [E,I,H] [E,H,I] */
+    /* activations: forward writes, backward reads (and overwrites when it replays later macrobatches) */
+    void *x_routed;        /* [MB, H] */
+    void *gate_shared, *up_shared, *hidden_shared;   /* [T, I] */
+    void *gate_routed, *up_routed, *hidden_routed;   /* [MB, I] */
+    void *y_shared;        /* [T, H]  forward out */
+    void *y_routed;        /* [MB, H] forward out */
+    /* backward outputs / scratch */
+    void *d_x_shared;      /* [T, H] */
+    void *d_x_routed;      /* [MB, H] */
+    void *d_gate_shared, *d_up_shared, *d_hidden_shared;   /* [T, I] */
+    void *d_gate_routed, *d_up_routed, *d_hidden_routed;   /* [MB, I] */
+    void *d_y_routed;      /* [MB, H] */
+    void *d_w_shared_gate, *d_w_shared_up, *d_w_shared_down;
+    void *d_w_routed_gate, *d_w_routed_up, *d_w_routed_down;
+    float* row_scratch;    /* fp32 [2 * MB]: router weight and router-weight gradient of every row (backward) */
+    uint32_t* status;      /* uint32 [1] */
+} mok_layer_args;
+
+/*
+ * BF16 forward: dispatch -> gate/up GEMM -> SwiGLU -> down GEMM -> combine, macrobatches last to first,
+ * plus the shared expert.  Replaces: dispatch_mlp_swiglu_combine_fwd_bf16, csrc/megakernel/forward.cuh:293-428
+ * (binding csrc/bindings.cu, op mok/ops.py:377-520).
+ */
+int mok_moe_forward_bf16(const mok_layer_args* args, mok_stream_t stream);
+
+/*
+ * BF16 forward without down projection / combine, macrobatch 0 only: rebuilds the saved context.
+ * Replaces: recompute_forward_context_bf16, csrc/megakernel/recompute_forward_context.cuh (op mok/ops.py:668-782).
+ */
+int mok_moe_recompute_bf16(const mok_layer_args* args, mok_stream_t stream);
+
+/*
+ * BF16 backward: dgrad and wgrad of routed and shared experts, router-weight gradient, reverse dispatch/combine.
+ * Replaces: dispatch_mlp_swiglu_combine_bwd_bf16, csrc/megakernel/backward.cuh:445-679 (op mok/ops.py:1079-1276),
+ * including zero_empty_routed_wgrads (csrc/utils.cuh:301-322).
+ */
+int mok_moe_backward_bf16(const mok_layer_args* args, mok_stream_t stream);
+
+/*
+ * One grouped GEMM launch, exposed for tests and profiling.  D[rows, N] = A[rows, K] * B[e]^T with rows grouped
+ * by `tokens_per_expert` (each a multiple of 256).  b_is_kn = 0: B is [E, N, K] (forward form, csrc/megakernel/
+ * grouped_gemm.cuh mm2_ABt); 1: B is [E, K, N] (dgrad form, mm2_AB).  tokens_per_expert may be NULL for a dense
+ * problem with `rows` rows and E = 1.
+ */
+int mok_grouped_gemm_bf16(const void* A, const void* B, void* D, const int32_t* tokens_per_expert,
+                          const int32_t* num_tokens, int num_experts, int rows, int N, int K, int b_is_kn,
+                          uint32_t* status, mok_stream_t stream);
+
+/*
+ * Weight-gradient form: D[e] [M, N] = A[rows_e, M]^T * B[rows_e, N] over the rows of expert e, in schedule order
+ * (fixed reduction order).  Replaces the mm2_AtB use of csrc/megakernel/grouped_gemm.cuh:153-167,241-243.
+ */
+int mok_grouped_wgrad_bf16(const void* A, const void* B, void* D, const int32_t* tokens_per_expert,
+                           const int32_t* num_tokens, int num_experts, int rows, int M, int N,
+                           uint32_t* status, mok_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MOK_B200_H */

@@ -1,0 +1,241 @@
+// Bandwidth-bound kernels of the MoE layer: SwiGLU forward / backward (with the router-weight gradient),
+// the fixed-order forward / backward epilogues, and zeroing the weight gradients of experts without tokens.
+#include "elementwise.cuh"
+
+namespace mok {
+namespace {
+
+__device__ __forceinline__ float sigmoid_fast(float x) { return 1.0f / (1.0f + __expf(-x)); }
+
+// hidden = silu(gate) * up on fp32 values of the stored bf16 gate / up (reference csrc/megakernel/swiglu.cuh:135-165)
+template <bool CLAMP>
+__device__ __forceinline__ uint32_t swiglu_pair(uint32_t g2, uint32_t u2, float limit) {
+    float2 g = unpack_bf16x2(g2), u = unpack_bf16x2(u2);
+    if (CLAMP) {
+        g.x = fminf(g.x, limit); g.y = fminf(g.y, limit);
+        u.x = fminf(fmaxf(u.x, -limit), limit); u.y = fminf(fmaxf(u.y, -limit), limit);
+    }
+    return pack_bf16x2(g.x * sigmoid_fast(g.x) * u.x, g.y * sigmoid_fast(g.y) * u.y);
+}
+
+template <bool CLAMP>
+__global__ void __launch_bounds__(256) swiglu_fwd_kernel(const uint4* __restrict__ gate, const uint4* __restrict__ up,
+                                                          uint4* __restrict__ hidden, const int* __restrict__ num_tokens,
+                                                          int dense_rows, int row_begin, int row_end, int vec_per_row,
+                                                          float limit) {
+    const int total = num_tokens != nullptr ? *num_tokens : dense_rows;
+    const int hi = min(row_end, total);
+    if (hi <= row_begin) return;
+    const long long n = static_cast<long long>(hi - row_begin) * vec_per_row;
+    const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+    for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride) {
+        const uint4 g = gate[i], u = up[i];
+        uint4 h;
+        h.x = swiglu_pair<CLAMP>(g.x, u.x, limit);
+        h.y = swiglu_pair<CLAMP>(g.y, u.y, limit);
+        h.z = swiglu_pair<CLAMP>(g.z, u.z, limit);
+        h.w = swiglu_pair<CLAMP>(g.w, u.w, limit);
+        hidden[i] = h;
+    }
+}
+
+// d_gate = dsilu(g) * u * dh, d_up = silu(g) * dh, zero where the forward clamp was active; returns
+// dh * silu(g) * u for the router-weight gradient (reference csrc/megakernel/swiglu.cuh:1-36).
+template <bool CLAMP>
+__device__ __forceinline__ float swiglu_bwd_pair(uint32_t g2, uint32_t u2, uint32_t dh2, float limit, uint32_t& dg2,
+                                                 uint32_t& du2) {
+    float2 g = unpack_bf16x2(g2), u = unpack_bf16x2(u2);
+    const float2 dh = unpack_bf16x2(dh2);
+    bool gx = true, gy = true, ux = true, uy = true;
+    if (CLAMP) {
+        gx = g.x <= limit; gy = g.y <= limit;
+        ux = u.x >= -limit && u.x <= limit; uy = u.y >= -limit && u.y <= limit;
+        g.x = fminf(g.x, limit); g.y = fminf(g.y, limit);
+        u.x = fminf(fmaxf(u.x, -limit), limit); u.y = fminf(fmaxf(u.y, -limit), limit);
+    }
+    const float sx = sigmoid_fast(g.x), sy = sigmoid_fast(g.y);
+    const float silu_x = g.x * sx, silu_y = g.y * sy;
+    const float dsx = (1.0f - silu_x) * sx + silu_x, dsy = (1.0f - silu_y) * sy + silu_y;
+    dg2 = pack_bf16x2(gx ? dsx * u.x * dh.x : 0.0f, gy ? dsy * u.y * dh.y : 0.0f);
+    du2 = pack_bf16x2(ux ? silu_x * dh.x : 0.0f, uy ? silu_y * dh.y : 0.0f);
+    return dh.x * (silu_x * u.x) + dh.y * (silu_y * u.y);
+}
+
+// One warp per row.  With row_weight != nullptr the warp also reduces sum_i dh*hidden over the row (lanes own
+// fixed column sets and the butterfly is fixed, so the result is reproducible) and stores it divided by the row's
+// router weight (0 when the weight is not positive): d_router_weight of that route.
+template <bool CLAMP>
+__global__ void __launch_bounds__(256) swiglu_bwd_kernel(const uint4* __restrict__ gate, const uint4* __restrict__ up,
+                                                          const uint4* __restrict__ d_hidden, uint4* __restrict__ d_gate,
+                                                          uint4* __restrict__ d_up, const int* __restrict__ num_tokens,
+                                                          int dense_rows, int row_begin, int row_end, int vec_per_row,
+                                                          float limit, const float* __restrict__ row_weight,
+                                                          float* __restrict__ row_grad) {
+    const int total = num_tokens != nullptr ? *num_tokens : dense_rows;
+    const int rows = min(row_end, total) - row_begin;
+    const int warps = (gridDim.x * blockDim.x) >> 5;
+    const int lane = threadIdx.x & 31;
+    for (int row = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; row < rows; row += warps) {
+        const size_t base = static_cast<size_t>(row) * vec_per_row;
+        float acc = 0.0f;
+        for (int v = lane; v < vec_per_row; v += 32) {
+            const uint4 g = gate[base + v], u = up[base + v], dh = d_hidden[base + v];
+            uint4 dg, du;
+            acc += swiglu_bwd_pair<CLAMP>(g.x, u.x, dh.x, limit, dg.x, du.x);
+            acc += swiglu_bwd_pair<CLAMP>(g.y, u.y, dh.y, limit, dg.y, du.y);
+            acc += swiglu_bwd_pair<CLAMP>(g.z, u.z, dh.z, limit, dg.z, du.z);
+            acc += swiglu_bwd_pair<CLAMP>(g.w, u.w, dh.w, limit, dg.w, du.w);
+            d_gate[base + v] = dg;
+            d_up[base + v] = du;
+        }
+        if (row_weight != nullptr) {
+#pragma unroll
+            for (int off = 16; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
+            if (lane == 0) {
+                const float w = row_weight[row];
+                row_grad[row] = w > 0.0f ? acc / w : 0.0f;
+            }
+        }
+    }
+}
+
+__device__ __forceinline__ void fma_vec(float (&acc)[8], uint4 v, float w) {
+    const float2 a = unpack_bf16x2(v.x), b = unpack_bf16x2(v.y), c = unpack_bf16x2(v.z), d = unpack_bf16x2(v.w);
+    acc[0] = fmaf(w, a.x, acc[0]); acc[1] = fmaf(w, a.y, acc[1]);
+    acc[2] = fmaf(w, b.x, acc[2]); acc[3] = fmaf(w, b.y, acc[3]);
+    acc[4] = fmaf(w, c.x, acc[4]); acc[5] = fmaf(w, c.y, acc[5]);
+    acc[6] = fmaf(w, d.x, acc[6]); acc[7] = fmaf(w, d.y, acc[7]);
+}
+
+// out[t] = bf16(shared[t] + sum_k w[t,k] * routed[t*K + k]), k ascending; WEIGHTED = false uses w = 1.
+template <bool WEIGHTED>
+__global__ void __launch_bounds__(256) epilogue_kernel(const uint4* __restrict__ shared, const uint4* __restrict__ routed,
+                                                        const float* __restrict__ weights, uint4* __restrict__ out,
+                                                        long long tokens, int vec_per_row, int topk) {
+    const long long n = tokens * vec_per_row;
+    const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+    for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride) {
+        const long long t = i / vec_per_row;
+        const int v = static_cast<int>(i - t * vec_per_row);
+        float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+        if (shared != nullptr) fma_vec(acc, shared[i], 1.0f);
+        const uint4* r = routed + (t * topk) * vec_per_row + v;
+        const float* w = weights + t * topk;
+        int k = 0;
+        for (; k + 4 <= topk; k += 4) {   // four rows in flight, accumulated in ascending k
+            const uint4 r0 = r[static_cast<long long>(k) * vec_per_row], r1 = r[static_cast<long long>(k + 1) * vec_per_row];
+            const uint4 r2 = r[static_cast<long long>(k + 2) * vec_per_row], r3 = r[static_cast<long long>(k + 3) * vec_per_row];
+            fma_vec(acc, r0, WEIGHTED ? w[k] : 1.0f);
+            fma_vec(acc, r1, WEIGHTED ? w[k + 1] : 1.0f);
+            fma_vec(acc, r2, WEIGHTED ? w[k + 2] : 1.0f);
+            fma_vec(acc, r3, WEIGHTED ? w[k + 3] : 1.0f);
+        }
+        for (; k < topk; ++k) fma_vec(acc, r[static_cast<long long>(k) * vec_per_row], WEIGHTED ? w[k] : 1.0f);
+        uint4 o;
+        o.x = pack_bf16x2(acc[0], acc[1]);
+        o.y = pack_bf16x2(acc[2], acc[3]);
+        o.z = pack_bf16x2(acc[4], acc[5]);
+        o.w = pack_bf16x2(acc[6], acc[7]);
+        out[i] = o;
+    }
+}
+
+__global__ void __launch_bounds__(256) zero_empty_kernel(const int* __restrict__ tokens_per_expert, uint4* a, uint4* b,
+                                                          uint4* c, long long vec_per_expert) {
+    const int e = blockIdx.y;
+    if (tokens_per_expert[e] != 0) return;
+    const uint4 z = make_uint4(0, 0, 0, 0);
+    const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+    for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < vec_per_expert; i += stride) {
+        a[e * vec_per_expert + i] = z;
+        b[e * vec_per_expert + i] = z;
+        c[e * vec_per_expert + i] = z;
+    }
+}
+
+int stream_grid(long long items, int threads) {
+    long long blocks = (items + threads - 1) / threads;
+    const long long cap = static_cast<long long>(sm_count()) * 16;
+    if (blocks > cap) blocks = cap;
+    return blocks < 1 ? 1 : static_cast<int>(blocks);
+}
+
+}  // namespace
+
+int launch_swiglu_fwd(const void* gate, const void* up, void* hidden, const int32_t* num_tokens, int dense_rows,
+                      int row_begin, int row_end, int intermediate, bool has_limit, float limit, cudaStream_t stream) {
+    if (intermediate % 8 != 0 || row_end <= row_begin) return MOK_ERR_INVALID_ARGUMENT;
+    const int vec = intermediate / 8;
+    const int grid = stream_grid(static_cast<long long>(row_end - row_begin) * vec, 256);
+    auto g = static_cast<const uint4*>(gate);
+    auto u = static_cast<const uint4*>(up);
+    auto h = static_cast<uint4*>(hidden);
+    if (has_limit)
+        swiglu_fwd_kernel<true><<<grid, 256, 0, stream>>>(g, u, h, num_tokens, dense_rows, row_begin, row_end, vec, limit);
+    else
+        swiglu_fwd_kernel<false><<<grid, 256, 0, stream>>>(g, u, h, num_tokens, dense_rows, row_begin, row_end, vec, limit);
+    MOK_LAUNCH_CHECK("swiglu_fwd_kernel");
+    return MOK_OK;
+}
+
+int launch_swiglu_bwd(const void* gate, const void* up, const void* d_hidden, void* d_gate, void* d_up,
+                      const int32_t* num_tokens, int dense_rows, int row_begin, int row_end, int intermediate,
+                      bool has_limit, float limit, const float* row_weight, float* row_grad, cudaStream_t stream) {
+    if (intermediate % 8 != 0 || row_end <= row_begin) return MOK_ERR_INVALID_ARGUMENT;
+    const int vec = intermediate / 8;
+    const int grid = stream_grid(static_cast<long long>(row_end - row_begin) * 32, 256);
+    auto g = static_cast<const uint4*>(gate);
+    auto u = static_cast<const uint4*>(up);
+    auto dh = static_cast<const uint4*>(d_hidden);
+    auto dg = static_cast<uint4*>(d_gate);
+    auto du = static_cast<uint4*>(d_up);
+    if (has_limit)
+        swiglu_bwd_kernel<true><<<grid, 256, 0, stream>>>(g, u, dh, dg, du, num_tokens, dense_rows, row_begin, row_end, vec,
+                                                         limit, row_weight, row_grad);
+    else
+        swiglu_bwd_kernel<false><<<grid, 256, 0, stream>>>(g, u, dh, dg, du, num_tokens, dense_rows, row_begin, row_end, vec,
+                                                          limit, row_weight, row_grad);
+    MOK_LAUNCH_CHECK("swiglu_bwd_kernel");
+    return MOK_OK;
+}
+
+int launch_zero_empty_wgrads(const int32_t* tokens_per_expert, int num_experts, void* a, void* b, void* c,
+                             long long elems_per_expert, cudaStream_t stream) {
+    if (elems_per_expert % 8 != 0) return MOK_ERR_INVALID_ARGUMENT;
+    dim3 grid(64, num_experts);
+    zero_empty_kernel<<<grid, 256, 0, stream>>>(tokens_per_expert, static_cast<uint4*>(a), static_cast<uint4*>(b),
+                                                static_cast<uint4*>(c), elems_per_expert / 8);
+    MOK_LAUNCH_CHECK("zero_empty_kernel");
+    return MOK_OK;
+}
+
+}  // namespace mok
+
+extern "C" int mok_fwd_epilogue(const void* y_shared, const void* combine_buffer, const float* topk_weights, void* out,
+                                int64_t num_local_tokens, int hidden, int topk, mok_stream_t stream) {
+    using namespace mok;
+    if (combine_buffer == nullptr || topk_weights == nullptr || out == nullptr || num_local_tokens <= 0 || hidden <= 0 ||
+        hidden % 8 != 0 || topk <= 0)
+        return MOK_ERR_INVALID_ARGUMENT;
+    const int vec = hidden / 8;
+    const int grid = stream_grid(num_local_tokens * vec, 256);
+    epilogue_kernel<true><<<grid, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+        static_cast<const uint4*>(y_shared), static_cast<const uint4*>(combine_buffer), topk_weights, static_cast<uint4*>(out),
+        num_local_tokens, vec, topk);
+    MOK_LAUNCH_CHECK("fwd_epilogue_kernel");
+    return MOK_OK;
+}
+
+extern "C" int mok_bwd_epilogue(const void* d_x_shared, const void* d_x_routed_buffer, void* out, int64_t num_local_tokens,
+                                int hidden, int topk, mok_stream_t stream) {
+    using namespace mok;
+    if (d_x_routed_buffer == nullptr || out == nullptr || num_local_tokens <= 0 || hidden <= 0 || hidden % 8 != 0 || topk <= 0)
+        return MOK_ERR_INVALID_ARGUMENT;
+    const int vec = hidden / 8;
+    const int grid = stream_grid(num_local_tokens * vec, 256);
+    epilogue_kernel<false><<<grid, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+        static_cast<const uint4*>(d_x_shared), static_cast<const uint4*>(d_x_routed_buffer), nullptr, static_cast<uint4*>(out),
+        num_local_tokens, vec, topk);
+    MOK_LAUNCH_CHECK("bwd_epilogue_kernel");
+    return MOK_OK;
+}

@@ -1,0 +1,532 @@
+// Grouped bf16 GEMM for sm_100a: tcgen05.mma with fp32 accumulators in tensor memory, operands staged in
+// shared memory by TMA (128-byte swizzle), persistent CTAs over a static tile list.
+//
+// One CTA = 6 warps:
+//   warp 0        TMA producer (one elected lane)
+//   warp 1        MMA issuer (one elected lane); owns the tensor-memory allocation
+//   warps 2..5    epilogue: tensor memory -> registers -> bf16 -> global (each warp owns 32 accumulator lanes)
+// Tile 128 x 256, K step 64, 4-stage operand ring (48 KB per stage), two 256-column accumulators in
+// tensor memory so the epilogue of tile i overlaps the main loop of tile i+1.
+//
+// Three forms (the roles the reference gives its grouped GEMM, csrc/megakernel/grouped_gemm.cuh):
+//   rows / B [E,N,K]   D[r,:] = A[r,:] B[e]^T          forward gate, up, down            (A, B K-major)
+//   rows / B [E,K,N]   D[r,:] = sum_s A_s[r,:] B_s[e]  dgrad down; dgrad gate+up (2 sets) (B MN-major)
+//   wgrad              D[e] (+)= A[rows_e,:]^T B[rows_e,:], K = rows of expert e          (A, B MN-major)
+// Every output element has exactly one writer and a fixed K order, so results are run-to-run identical.
+#include "grouped_gemm.cuh"
+
+namespace mok {
+namespace {
+
+constexpr int BM = 128;
+constexpr int BN = 256;
+constexpr int BK = 64;
+constexpr int STAGES = 4;
+constexpr int A_TILE_BYTES = BM * BK * 2;            // 16 KB
+constexpr int B_TILE_BYTES = BN * BK * 2;            // 32 KB
+constexpr int STAGE_BYTES = A_TILE_BYTES + B_TILE_BYTES;
+constexpr int CHUNK_BYTES = 64 * BK * 2;             // one 64(MN) x 64(K) block of an MN-major operand: 8 KB
+constexpr int NUM_THREADS = 192;
+constexpr int TMEM_COLS = 512;
+constexpr int MODE_ROWS = 0;
+constexpr int MODE_WGRAD = 1;
+
+struct KernelParams {
+    const int32_t* tokens_per_expert;
+    const int32_t* num_tokens;
+    int num_experts;
+    int dense_rows;
+    int row_begin, row_end;
+    int n_blocks;     // rows: N / 256 per output set; wgrad: N / 256
+    int m_blocks_w;   // wgrad: M / 128
+    int k_blocks;     // rows: K / 64 per operand set
+    int n_sets;       // rows: output sets sharing A (1 or 2)
+    int k_sets;       // rows: operand sets accumulated into one output (1 or 2)
+    bf16* D0;
+    bf16* D1;
+    long long ldd;
+    long long d_expert_stride;
+    uint32_t* status;
+};
+
+struct Tile {
+    int expert;
+    int row0;       // rows: first schedule row of the tile; wgrad: first K row
+    int m0, n0;     // wgrad: output row / column offset; rows: n0 = column offset
+    int set;        // rows: output set
+    int k_blocks;   // K steps of 64
+    int accumulate; // wgrad: add to what is already stored
+};
+
+struct SharedLayout {
+    // dynamic shared memory, 1024-byte aligned base:
+    //   [0, STAGES*STAGE_BYTES)  operand ring
+    //   then barriers, bookkeeping, and the expert row prefix
+    static constexpr int kBarrierOffset = STAGES * STAGE_BYTES;
+    static constexpr int kFull = kBarrierOffset;                  // STAGES x 8 B
+    static constexpr int kEmpty = kFull + 8 * STAGES;             // STAGES x 8 B
+    static constexpr int kTmemFull = kEmpty + 8 * STAGES;         // 2 x 8 B
+    static constexpr int kTmemEmpty = kTmemFull + 16;             // 2 x 8 B
+    static constexpr int kTmemPtr = kTmemEmpty + 16;              // 4 B
+    static constexpr int kAbort = kTmemPtr + 4;                   // 4 B
+    static constexpr int kCum = kAbort + 4 + 8;                   // (E + 1) x 4 B
+};
+
+template <int MODE>
+__device__ __forceinline__ bool decode_tile(const KernelParams& p, const int* cum, int lo, int hi, int t, Tile& tile) {
+    if (MODE == MODE_ROWS) {
+        const int per_m = p.n_blocks * p.n_sets;
+        const int mt = t / per_m;
+        const int rem = t - mt * per_m;
+        tile.set = rem / p.n_blocks;
+        tile.n0 = (rem - tile.set * p.n_blocks) * BN;
+        tile.row0 = lo + mt * BM;
+        tile.m0 = 0;
+        int e = 0;
+        if (p.tokens_per_expert != nullptr) {   // largest e with cum[e] <= row0
+            int a = 0, b = p.num_experts;
+            while (b - a > 1) {
+                const int mid = (a + b) >> 1;
+                if (cum[mid] <= tile.row0) a = mid; else b = mid;
+            }
+            e = a;
+        }
+        tile.expert = e;
+        tile.k_blocks = p.k_blocks * p.k_sets;
+        tile.accumulate = 0;
+        return true;
+    } else {
+        const int per_e = p.m_blocks_w * p.n_blocks;
+        const int e = t / per_e;
+        const int rem = t - e * per_e;
+        const int mi = rem / p.n_blocks;
+        tile.expert = e;
+        tile.m0 = mi * BM;
+        tile.n0 = (rem - mi * p.n_blocks) * BN;
+        tile.set = 0;
+        const int ks = max(cum[e], lo);
+        const int ke = min(cum[e + 1], hi);
+        tile.row0 = ks;
+        tile.k_blocks = ke > ks ? (ke - ks) / BK : 0;
+        tile.accumulate = cum[e] < lo ? 1 : 0;
+        return tile.k_blocks > 0;
+    }
+}
+
+__device__ __forceinline__ void store_row_chunk(bf16* dst, const uint32_t (&acc)[32], bool accumulate) {
+    uint4* out = reinterpret_cast<uint4*>(dst);
+#pragma unroll
+    for (int v = 0; v < 4; ++v) {
+        float f[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) f[i] = __uint_as_float(acc[v * 8 + i]);
+        if (accumulate) {
+            const uint4 old = out[v];
+            const float2 o0 = unpack_bf16x2(old.x), o1 = unpack_bf16x2(old.y), o2 = unpack_bf16x2(old.z), o3 = unpack_bf16x2(old.w);
+            f[0] += o0.x; f[1] += o0.y; f[2] += o1.x; f[3] += o1.y;
+            f[4] += o2.x; f[5] += o2.y; f[6] += o3.x; f[7] += o3.y;
+        }
+        uint4 w;
+        w.x = pack_bf16x2(f[0], f[1]);
+        w.y = pack_bf16x2(f[2], f[3]);
+        w.z = pack_bf16x2(f[4], f[5]);
+        w.w = pack_bf16x2(f[6], f[7]);
+        out[v] = w;
+    }
+}
+
+template <int MODE, bool B_MN>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__ CUtensorMap tmB0,
+                    const __grid_constant__ CUtensorMap tmA1, const __grid_constant__ CUtensorMap tmB1,
+                    const KernelParams p) {
+    constexpr bool A_MN = (MODE == MODE_WGRAD);
+    static_assert(MODE == MODE_ROWS || B_MN, "the weight-gradient form reads both operands MN-major");
+
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+    const uint32_t bar_full = smem_base + SharedLayout::kFull;
+    const uint32_t bar_empty = smem_base + SharedLayout::kEmpty;
+    const uint32_t bar_tmem_full = smem_base + SharedLayout::kTmemFull;
+    const uint32_t bar_tmem_empty = smem_base + SharedLayout::kTmemEmpty;
+    volatile uint32_t* tmem_ptr_slot = reinterpret_cast<volatile uint32_t*>(smem_gen + SharedLayout::kTmemPtr);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_gen + SharedLayout::kAbort);
+    int* cum = reinterpret_cast<int*>(smem_gen + SharedLayout::kCum);
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+
+    // ---- set-up ---------------------------------------------------------------------------------------
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(bar_full + 8 * s, 1);
+            mbar_init(bar_empty + 8 * s, 1);
+        }
+        for (int s = 0; s < 2; ++s) {
+            mbar_init(bar_tmem_full + 8 * s, 1);
+            mbar_init(bar_tmem_empty + 8 * s, 4);
+        }
+        *abort_flag = 0;
+        mbar_fence_init();
+        tma_prefetch_desc(&tmA0);
+        tma_prefetch_desc(&tmB0);
+        if (p.k_sets > 1) tma_prefetch_desc(&tmA1);
+        if (p.k_sets > 1 || p.n_sets > 1) tma_prefetch_desc(&tmB1);
+    }
+    if (warp == 1) {
+        tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_ptr_slot)), TMEM_COLS);
+        tmem_relinquish();
+    }
+    if (warp == 2) {   // inclusive prefix of the per-expert row counts -> cum[0..E]
+        if (p.tokens_per_expert == nullptr) {
+            if (lane == 0) { cum[0] = 0; cum[1] = p.dense_rows; }
+        } else {
+            int carry = 0;
+            if (lane == 0) cum[0] = 0;
+            for (int base = 0; base < p.num_experts; base += 32) {
+                const int idx = base + lane;
+                int v = idx < p.num_experts ? p.tokens_per_expert[idx] : 0;
+#pragma unroll
+                for (int off = 1; off < 32; off <<= 1) {
+                    const int n = __shfl_up_sync(0xffffffffu, v, off);
+                    if (lane >= off) v += n;
+                }
+                if (idx < p.num_experts) cum[idx + 1] = carry + v;
+                carry += __shfl_sync(0xffffffffu, v, 31);
+            }
+        }
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = *tmem_ptr_slot;
+
+    const int total_rows = p.tokens_per_expert == nullptr ? p.dense_rows : *p.num_tokens;
+    const int lo = p.row_begin;
+    const int hi = min(p.row_end, total_rows);
+    int total_tiles;
+    if (MODE == MODE_ROWS) total_tiles = hi > lo ? ((hi - lo) / BM) * p.n_blocks * p.n_sets : 0;
+    else total_tiles = hi > lo ? p.num_experts * p.m_blocks_w * p.n_blocks : 0;
+
+    constexpr uint32_t kIdesc = umma_idesc_bf16(BM, BN, A_MN, B_MN);
+
+    if (warp == 0) {
+        // ---- TMA producer ---------------------------------------------------------------------------
+        int stage = 0;
+        uint32_t phase = 0;
+        bool ok = true;
+        for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+            Tile tile;
+            if (!decode_tile<MODE>(p, cum, lo, hi, t, tile)) continue;
+            for (int kb = 0; kb < tile.k_blocks; ++kb) {
+                ok = mbar_wait(bar_empty + 8 * stage, phase ^ 1u, abort_flag, p.status);
+                if (!ok) break;
+                if (lane == 0) {
+                    const uint32_t full = bar_full + 8 * stage;
+                    const uint32_t a_dst = smem_base + stage * STAGE_BYTES;
+                    const uint32_t b_dst = a_dst + A_TILE_BYTES;
+                    mbar_expect_tx(full, STAGE_BYTES);
+                    if (MODE == MODE_ROWS) {
+                        const int kset = kb >= p.k_blocks ? 1 : 0;
+                        const int kk = (kb - kset * p.k_blocks) * BK;
+                        tma_load_4d(a_dst, kset ? &tmA1 : &tmA0, full, kk, tile.row0 - p.row_begin, 0, 0);
+                        const CUtensorMap* bmap = (kset || tile.set) ? &tmB1 : &tmB0;
+                        if (!B_MN) {
+                            tma_load_4d(b_dst, bmap, full, kk, tile.n0, tile.expert, 0);
+                        } else {
+#pragma unroll
+                            for (int c = 0; c < BN / 64; ++c)
+                                tma_load_4d(b_dst + c * CHUNK_BYTES, bmap, full, tile.n0 + c * 64, kk, tile.expert, 0);
+                        }
+                    } else {
+                        const int krow = tile.row0 + kb * BK - p.row_begin;
+#pragma unroll
+                        for (int c = 0; c < BM / 64; ++c)
+                            tma_load_4d(a_dst + c * CHUNK_BYTES, &tmA0, full, tile.m0 + c * 64, krow, 0, 0);
+#pragma unroll
+                        for (int c = 0; c < BN / 64; ++c)
+                            tma_load_4d(b_dst + c * CHUNK_BYTES, &tmB0, full, tile.n0 + c * 64, krow, 0, 0);
+                    }
+                }
+                __syncwarp();
+                if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+            }
+        }
+    } else if (warp == 1) {
+        // ---- MMA issuer -----------------------------------------------------------------------------
+        int stage = 0;
+        uint32_t phase = 0;
+        int iter = 0;
+        bool ok = true;
+        // descriptor steps per 16-wide K slice (units of 16 bytes): 32 B inside a K-major swizzle row,
+        // two 8-row groups (2 KB) of an MN-major tile
+        constexpr uint32_t kAStep = A_MN ? 128u : 2u;
+        constexpr uint32_t kBStep = B_MN ? 128u : 2u;
+        for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+            Tile tile;
+            if (!decode_tile<MODE>(p, cum, lo, hi, t, tile)) continue;
+            const int acc = iter & 1;
+            const uint32_t acc_phase = (iter >> 1) & 1u;
+            ok = mbar_wait(bar_tmem_empty + 8 * acc, acc_phase ^ 1u, abort_flag, p.status);
+            if (!ok) break;
+            tc_fence_after_sync();
+            const uint32_t d_tmem = tmem_base + acc * BN;
+            for (int kb = 0; kb < tile.k_blocks; ++kb) {
+                ok = mbar_wait(bar_full + 8 * stage, phase, abort_flag, p.status);
+                if (!ok) break;
+                tc_fence_after_sync();
+                if (lane == 0) {
+                    const uint32_t a_addr = smem_base + stage * STAGE_BYTES;
+                    const uint32_t b_addr = a_addr + A_TILE_BYTES;
+                    const uint64_t a_desc = A_MN ? umma_smem_desc(a_addr, CHUNK_BYTES, 1024) : umma_smem_desc(a_addr, 16, 1024);
+                    const uint64_t b_desc = B_MN ? umma_smem_desc(b_addr, CHUNK_BYTES, 1024) : umma_smem_desc(b_addr, 16, 1024);
+#pragma unroll
+                    for (int k = 0; k < BK / 16; ++k)
+                        umma_bf16(d_tmem, a_desc + k * kAStep, b_desc + k * kBStep, kIdesc, (kb | k) != 0 ? 1u : 0u);
+                    umma_commit(bar_empty + 8 * stage);                       // frees the operand stage
+                    if (kb == tile.k_blocks - 1) umma_commit(bar_tmem_full + 8 * acc);   // accumulator complete
+                }
+                __syncwarp();
+                if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+            }
+            ++iter;
+        }
+    } else {
+        // ---- epilogue -------------------------------------------------------------------------------
+        const int quarter = warp & 3;                 // tensor-memory lanes [32*quarter, 32*quarter + 32)
+        const int row_in_tile = quarter * 32 + lane;
+        int iter = 0;
+        bool ok = true;
+        for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+            Tile tile;
+            if (!decode_tile<MODE>(p, cum, lo, hi, t, tile)) continue;
+            const int acc = iter & 1;
+            const uint32_t acc_phase = (iter >> 1) & 1u;
+            ok = mbar_wait(bar_tmem_full + 8 * acc, acc_phase, abort_flag, p.status);
+            if (!ok) break;
+            tc_fence_after_sync();
+            bf16* out;
+            if (MODE == MODE_ROWS)
+                out = (tile.set ? p.D1 : p.D0) + static_cast<long long>(tile.row0 - p.row_begin + row_in_tile) * p.ldd + tile.n0;
+            else
+                out = p.D0 + static_cast<long long>(tile.expert) * p.d_expert_stride +
+                      static_cast<long long>(tile.m0 + row_in_tile) * p.ldd + tile.n0;
+            const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * BN;
+#pragma unroll 1
+            for (int c = 0; c < BN / 32; ++c) {
+                uint32_t v[32];
+                tmem_ld_32x32(taddr + c * 32, v);
+                tmem_ld_wait();
+                store_row_chunk(out + c * 32, v, tile.accumulate != 0);
+            }
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_tmem_empty + 8 * acc);
+            ++iter;
+        }
+    }
+
+    // ---- teardown -------------------------------------------------------------------------------------
+    if (*abort_flag) {   // give copies that are still in flight time to land before shared memory is released
+        for (int i = 0; i < 64; ++i) __nanosleep(2000);
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after_sync();
+        tmem_dealloc(tmem_base, TMEM_COLS);
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// Host side
+// ---------------------------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (fn == nullptr) {
+        void* sym = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres) == cudaSuccess &&
+            qres == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(sym);
+    }
+    return fn;
+}
+
+// Rank-4 bf16 map over a row-major [d2][d1][d0] array (d0 contiguous); box = {b0, b1, 1, 1}.
+int make_map(CUtensorMap* map, const void* base, uint64_t d0, uint64_t d1, uint64_t d2, uint32_t b0, uint32_t b1) {
+    EncodeTiledFn fn = encode_fn();
+    if (fn == nullptr) {
+        set_last_error("cuTensorMapEncodeTiled unavailable", cudaErrorNotSupported);
+        return MOK_ERR_CUDA;
+    }
+    cuuint64_t dims[4] = {d0, d1, d2, 1};
+    cuuint64_t strides[3] = {d0 * 2, d0 * d1 * 2, d0 * d1 * d2 * 2};
+    cuuint32_t box[4] = {b0, b1, 1, 1};
+    cuuint32_t estr[4] = {1, 1, 1, 1};
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        set_last_error("cuTensorMapEncodeTiled failed", cudaErrorInvalidValue);
+        return MOK_ERR_CUDA;
+    }
+    return MOK_OK;
+}
+
+size_t smem_bytes(int num_experts) {
+    return 1024 + SharedLayout::kCum + 4 * (static_cast<size_t>(num_experts) + 2);
+}
+
+template <int MODE, bool B_MN>
+int launch(const CUtensorMap& a0, const CUtensorMap& b0, const CUtensorMap& a1, const CUtensorMap& b1,
+           const KernelParams& kp, int max_tiles, cudaStream_t stream) {
+    auto kernel = grouped_gemm_kernel<MODE, B_MN>;
+    const size_t smem = smem_bytes(kp.num_experts);
+    static size_t configured[16] = {0};   // per device
+    int dev = 0;
+    MOK_CUDA_CHECK(cudaGetDevice(&dev));
+    if (dev < 16 && configured[dev] < smem) {
+        MOK_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 232448 - 1024));
+        configured[dev] = 232448;
+    }
+    int grid = sm_count();
+    if (max_tiles < grid) grid = max_tiles;
+    if (grid <= 0) return MOK_OK;
+    kernel<<<grid, NUM_THREADS, smem, stream>>>(a0, b0, a1, b1, kp);
+    MOK_LAUNCH_CHECK("grouped_gemm_kernel");
+    return MOK_OK;
+}
+
+int check_problem(const GemmProblem& pb) {
+    if (pb.num_experts < 1 || pb.num_experts > MOK_MAX_LOCAL_EXPERTS) return MOK_ERR_TOO_LARGE;
+    if (pb.row_begin < 0 || pb.row_end < pb.row_begin || (pb.row_begin % 256) != 0 || (pb.row_end % 128) != 0)
+        return MOK_ERR_INVALID_ARGUMENT;
+    if (pb.buffer_rows <= 0) return MOK_ERR_INVALID_ARGUMENT;
+    if (pb.tokens_per_expert == nullptr && (pb.num_experts != 1 || pb.dense_rows % 128 != 0)) return MOK_ERR_INVALID_ARGUMENT;
+    if (pb.tokens_per_expert != nullptr && pb.num_tokens == nullptr) return MOK_ERR_INVALID_ARGUMENT;
+    return MOK_OK;
+}
+
+KernelParams base_params(const GemmProblem& pb) {
+    KernelParams kp{};
+    kp.tokens_per_expert = pb.tokens_per_expert;
+    kp.num_tokens = pb.num_tokens;
+    kp.num_experts = pb.num_experts;
+    kp.dense_rows = pb.dense_rows;
+    kp.row_begin = pb.row_begin;
+    kp.row_end = pb.row_end;
+    kp.n_sets = 1;
+    kp.k_sets = 1;
+    kp.status = pb.status;
+    return kp;
+}
+
+}  // namespace
+
+int launch_rows_gemm(const GemmProblem& pb, const void* A, int K, const void* B0, const void* B1, void* D0, void* D1,
+                     int N, bool b_is_kn, cudaStream_t stream) {
+    int rc = check_problem(pb);
+    if (rc != MOK_OK) return rc;
+    if (K <= 0 || N <= 0 || K % BK != 0 || N % BN != 0) return MOK_ERR_INVALID_ARGUMENT;
+    const int n_sets = (B1 != nullptr) ? 2 : 1;
+    CUtensorMap a0, b0, b1;
+    if ((rc = make_map(&a0, A, K, pb.buffer_rows, 1, BK, BM)) != MOK_OK) return rc;
+    if (!b_is_kn) {
+        if ((rc = make_map(&b0, B0, K, N, pb.num_experts, BK, BN)) != MOK_OK) return rc;
+        if ((rc = make_map(&b1, n_sets == 2 ? B1 : B0, K, N, pb.num_experts, BK, BN)) != MOK_OK) return rc;
+    } else {
+        if ((rc = make_map(&b0, B0, N, K, pb.num_experts, 64, BK)) != MOK_OK) return rc;
+        if ((rc = make_map(&b1, n_sets == 2 ? B1 : B0, N, K, pb.num_experts, 64, BK)) != MOK_OK) return rc;
+    }
+    KernelParams kp = base_params(pb);
+    kp.n_blocks = N / BN;
+    kp.k_blocks = K / BK;
+    kp.n_sets = n_sets;
+    kp.D0 = static_cast<bf16*>(D0);
+    kp.D1 = static_cast<bf16*>(D1);
+    kp.ldd = N;
+    const int window = pb.row_end - pb.row_begin;
+    const int max_tiles = (window / BM) * kp.n_blocks * n_sets;
+    return b_is_kn ? launch<MODE_ROWS, true>(a0, b0, a0, b1, kp, max_tiles, stream)
+                   : launch<MODE_ROWS, false>(a0, b0, a0, b1, kp, max_tiles, stream);
+}
+
+int launch_rows_gemm_dual(const GemmProblem& pb, const void* A0, const void* A1, int K, const void* B0, const void* B1,
+                          void* D, int N, cudaStream_t stream) {
+    int rc = check_problem(pb);
+    if (rc != MOK_OK) return rc;
+    if (K <= 0 || N <= 0 || K % BK != 0 || N % BN != 0) return MOK_ERR_INVALID_ARGUMENT;
+    CUtensorMap a0, a1, b0, b1;
+    if ((rc = make_map(&a0, A0, K, pb.buffer_rows, 1, BK, BM)) != MOK_OK) return rc;
+    if ((rc = make_map(&a1, A1, K, pb.buffer_rows, 1, BK, BM)) != MOK_OK) return rc;
+    if ((rc = make_map(&b0, B0, N, K, pb.num_experts, 64, BK)) != MOK_OK) return rc;
+    if ((rc = make_map(&b1, B1, N, K, pb.num_experts, 64, BK)) != MOK_OK) return rc;
+    KernelParams kp = base_params(pb);
+    kp.n_blocks = N / BN;
+    kp.k_blocks = K / BK;
+    kp.k_sets = 2;
+    kp.D0 = static_cast<bf16*>(D);
+    kp.D1 = nullptr;
+    kp.ldd = N;
+    const int window = pb.row_end - pb.row_begin;
+    return launch<MODE_ROWS, true>(a0, b0, a1, b1, kp, (window / BM) * kp.n_blocks, stream);
+}
+
+int launch_wgrad_gemm(const GemmProblem& pb, const void* A, int M, const void* B, int N, void* D, cudaStream_t stream) {
+    int rc = check_problem(pb);
+    if (rc != MOK_OK) return rc;
+    if (M <= 0 || N <= 0 || M % BM != 0 || N % BN != 0) return MOK_ERR_INVALID_ARGUMENT;
+    CUtensorMap a0, b0;
+    if ((rc = make_map(&a0, A, M, pb.buffer_rows, 1, 64, BK)) != MOK_OK) return rc;
+    if ((rc = make_map(&b0, B, N, pb.buffer_rows, 1, 64, BK)) != MOK_OK) return rc;
+    KernelParams kp = base_params(pb);
+    kp.n_blocks = N / BN;
+    kp.m_blocks_w = M / BM;
+    kp.D0 = static_cast<bf16*>(D);
+    kp.ldd = N;
+    kp.d_expert_stride = static_cast<long long>(M) * N;
+    return launch<MODE_WGRAD, true>(a0, b0, a0, b0, kp, pb.num_experts * kp.m_blocks_w * kp.n_blocks, stream);
+}
+
+}  // namespace mok
+
+// ---------------------------------------------------------------------------------------------------------
+// C ABI: single launches, for tests and profiling
+// ---------------------------------------------------------------------------------------------------------
+extern "C" int mok_grouped_gemm_bf16(const void* A, const void* B, void* D, const int32_t* tokens_per_expert,
+                                     const int32_t* num_tokens, int num_experts, int rows, int N, int K, int b_is_kn,
+                                     uint32_t* status, mok_stream_t stream) {
+    if (A == nullptr || B == nullptr || D == nullptr || rows <= 0 || rows % 128 != 0) return MOK_ERR_INVALID_ARGUMENT;
+    mok::GemmProblem pb;
+    pb.tokens_per_expert = tokens_per_expert;
+    pb.num_tokens = num_tokens;
+    pb.num_experts = tokens_per_expert ? num_experts : 1;
+    pb.dense_rows = tokens_per_expert ? 0 : rows;
+    pb.row_begin = 0;
+    pb.row_end = rows;
+    pb.buffer_rows = rows;
+    pb.status = status;
+    return mok::launch_rows_gemm(pb, A, K, B, nullptr, D, nullptr, N, b_is_kn != 0, reinterpret_cast<cudaStream_t>(stream));
+}
+
+extern "C" int mok_grouped_wgrad_bf16(const void* A, const void* B, void* D, const int32_t* tokens_per_expert,
+                                      const int32_t* num_tokens, int num_experts, int rows, int M, int N,
+                                      uint32_t* status, mok_stream_t stream) {
+    if (A == nullptr || B == nullptr || D == nullptr || rows <= 0 || rows % 128 != 0) return MOK_ERR_INVALID_ARGUMENT;
+    mok::GemmProblem pb;
+    pb.tokens_per_expert = tokens_per_expert;
+    pb.num_tokens = num_tokens;
+    pb.num_experts = tokens_per_expert ? num_experts : 1;
+    pb.dense_rows = tokens_per_expert ? 0 : rows;
+    pb.row_begin = 0;
+    pb.row_end = rows;
+    pb.buffer_rows = rows;
+    pb.status = status;
+    return mok::launch_wgrad_gemm(pb, A, M, B, N, D, reinterpret_cast<cudaStream_t>(stream));
+}

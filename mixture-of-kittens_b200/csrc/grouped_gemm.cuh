@@ -1,0 +1,34 @@
+// Host-side interface of the tcgen05 grouped GEMM (grouped_gemm.cu), used by the fused-layer entry points.
+#pragma once
+
+#include "mok_common.cuh"
+
+namespace mok {
+
+// A grouped-GEMM problem over schedule rows.  Rows are grouped by expert: expert e owns the contiguous,
+// 256-aligned row range [cum[e], cum[e+1]) given by `tokens_per_expert`; only rows inside the window
+// [row_begin, min(row_end, *num_tokens)) are touched, and activation buffers are indexed by (row - row_begin)
+// (the macrobatch ring).  A dense problem (one expert, `dense_rows` rows) has tokens_per_expert == nullptr.
+struct GemmProblem {
+    const int32_t* tokens_per_expert = nullptr;
+    const int32_t* num_tokens = nullptr;
+    int num_experts = 1;
+    int dense_rows = 0;
+    int row_begin = 0, row_end = 0;
+    int buffer_rows = 0;   // rows of the activation buffers (macrobatch size, or T for a dense problem)
+    uint32_t* status = nullptr;
+};
+
+// D_s[row, :] = A[row, :K] * B_s[e]^T for s < n_sets (two sets share A: gate and up projections).
+// b_is_kn = false: B_s is [E, N, K];  true: B_s is [E, K, N].
+int launch_rows_gemm(const GemmProblem& pb, const void* A, int K, const void* B0, const void* B1, void* D0, void* D1,
+                     int N, bool b_is_kn, cudaStream_t stream);
+
+// D[row, :] = A0[row, :K] * B0[e] + A1[row, :K] * B1[e] with B_s stored [E, K, N] (gate+up input gradient).
+int launch_rows_gemm_dual(const GemmProblem& pb, const void* A0, const void* A1, int K, const void* B0, const void* B1,
+                          void* D, int N, cudaStream_t stream);
+
+// D[e] [M, N] (+)= A[rows_e, M]^T * B[rows_e, N]; accumulates when expert e's rows began before row_begin.
+int launch_wgrad_gemm(const GemmProblem& pb, const void* A, int M, const void* B, int N, void* D, cudaStream_t stream);
+
+}  // namespace mok

@@ -1,0 +1,9 @@
+"""B200-native MoE kernel library with the `mok` interface: `mok.functional` (workspaces, schedules, forward /
+backward) over `mok.ops` (twelve `torch.ops.mok.*` custom ops) over libmok_b200.so (hand-written sm_100a CUDA)."""
+from . import ops
+from . import _fake_impls  # noqa: F401  (registers shape functions for torch.compile / FakeTensor)
+from . import functional
+
+__version__ = "0.1.0"
+
+__all__ = ["__version__", "functional", "ops"]
