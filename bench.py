@@ -1,0 +1,341 @@
+"""Benchmark of the expert-parallel MoE layer, forward + backward (tokens/s).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload c2|c1|c0|tiny]
+
+One step = build_schedule + forward + backward of one MoE layer over one batch of synthetic tokens through
+`mok.functional`.  The default workload is the DeepSeek-V3-shaped layer (32768 tokens per rank, hidden 7168,
+256 routed experts of intermediate 2048 sharded over the N ranks, top-8, one shared expert).  Rank 0 prints one
+JSON line.  Under torchrun (N > 1) every rank runs one GPU; times are the maximum over ranks.
+
+`--impl reference` times the CPU restatement of the reference math (oracle/) on the host cores, on a bounded
+sample of the same layer shape; that leg never touches the GPU library.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+for _p in (ROOT, os.path.join(ROOT, "mixture-of-kittens_b200")):
+    if _p not in sys.path:
+        sys.path.insert(0, _p)
+
+WORKLOADS = {
+    # name: tokens/rank, hidden, experts (global), intermediate, topk, weight std, bias std
+    "c2": dict(T=32768, H=7168, E=256, I=2048, K=8, std=0.006, bias=0.0, label="deepseek-v3-shaped bf16"),
+    "c1": dict(T=16384, H=2048, E=128, I=768, K=8, std=0.02, bias=0.5, label="qwen3-moe-shaped bf16"),
+    "c0": dict(T=2048, H=512, E=8, I=1024, K=2, std=0.02, bias=0.0, label="cpu-plumbing shape"),
+    "tiny": dict(T=512, H=256, E=8, I=256, K=2, std=0.02, bias=0.0, label="tiny"),
+}
+
+
+def flops_per_token(w) -> float:
+    """Algorithmic FLOPs of forward + backward per token: 18*K*H*I for the routed experts (3 GEMMs forward, 6
+    backward, 2*H*I each) plus 18*H*I for the shared expert.  Padding rows and replayed GEMMs are not counted."""
+    return 18.0 * (w["K"] + 1) * w["H"] * w["I"]
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        return dict(burst=float(p["bf16_tflops"]), sustained=float(p.get("bf16_tflops_sustained", p["bf16_tflops"])),
+                    hbm=float(p["hbm_gbs"]), source="measured")
+    return dict(burst=1590.0, sustained=1400.0, hbm=6650.0, source="fallback")
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons with nvidia-smi while the timed region runs."""
+    QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.samples, self.proc = index, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                                          "-i", str(self.index), "-lms", "200"], stdout=subprocess.PIPE, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.samples.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": []}
+        self.proc.terminate()
+        time.sleep(0.05)
+        clocks, reasons, mx = [], set(), None
+        for s in self.samples:
+            try:
+                clocks.append(float(s[0]))
+                mx = float(s[1])
+            except (ValueError, IndexError):
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), s[2:6]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(clocks) if clocks else None, "sm_max_mhz": mx, "reasons": sorted(reasons),
+                "samples": len(clocks)}
+
+
+# ------------------------------------------------------------------------------------------------------------
+# CPU arm: the oracle's restatement of the reference math, timed on the host cores
+# ------------------------------------------------------------------------------------------------------------
+def cpu_sample(w, tokens: int, experts: int, steps: int, warmup: int):
+    """Times fwd+bwd of a bounded sample: `tokens` tokens, `experts` experts, same H / I / K as the workload."""
+    import torch
+    from oracle import moe_oracle as O
+    inp = O.make_rank_inputs(0, experts, experts, min(w["K"], experts), tokens, w["H"], w["I"], seed=0, weight_std=w["std"])
+    times = []
+    for i in range(warmup + steps):
+        t0 = time.perf_counter()
+        O.moe_layer_oracle([inp])
+        if i >= warmup:
+            times.append(time.perf_counter() - t0)
+    sec = statistics.median(times)
+    return tokens / sec, sec, torch.get_num_threads()
+
+
+def cpu_sample_size(w):
+    # about 2e11..6e11 FLOP per pass: seconds on a few host cores
+    budget = 4e11
+    tokens = int(max(64, min(2048, budget / flops_per_token(w))))
+    tokens = max(64, tokens // 64 * 64)
+    return tokens, min(w["E"], 8)
+
+
+def run_reference_arm(args, w):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    tokens, experts = cpu_sample_size(w)
+    tps, sec, cores = cpu_sample(w, tokens, experts, max(1, args.steps), min(args.warmup, 1))
+    sample = f"{tokens} tokens, {experts} experts, H={w['H']} I={w['I']} top-{min(w['K'], experts)}, fp32 math with bf16 rounding points"
+    line = {
+        "impl": "reference", "metric": "moe_layer_fwd_bwd_tokens_per_s", "value": tps, "unit": "tokens/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": sec * 1e3,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": w["label"], "tokens_per_rank": w["T"], "hidden": w["H"], "experts": w["E"],
+                   "intermediate": w["I"], "topk": w["K"], "shared_expert": True},
+        "cpu_baseline": {"value": tps, "unit": "tokens/s", "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": tps, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ------------------------------------------------------------------------------------------------------------
+# GPU arm
+# ------------------------------------------------------------------------------------------------------------
+def make_gpu_inputs(w, e_loc: int, rank: int, dev):
+    """Seeded synthetic layer: x, dy ~ N(0,1); weights ~ N(0, std); logits = x W_r (+ bias ~ N(0, bias));
+    top-k routing with softmax over the selected logits (renormalised weights)."""
+    import torch
+    g = torch.Generator(device=dev).manual_seed(0 + rank)
+    gw = torch.Generator(device=dev).manual_seed(12345)          # router and bias are shared by all ranks
+    T, H, E, I, K = w["T"], w["H"], w["E"], w["I"], w["K"]
+    bf = dict(device=dev, dtype=torch.bfloat16)
+    x = torch.randn(T, H, generator=g, **bf)
+    dy = torch.randn(T, H, generator=g, **bf)
+    w_r = torch.randn(H, E, generator=gw, device=dev) * w["std"]
+    logits = x.float() @ w_r
+    if w["bias"] > 0:
+        logits += torch.randn(E, generator=gw, device=dev) * w["bias"]
+    vals, topk = torch.topk(logits, K, dim=1)
+    rw = torch.softmax(vals, dim=-1).contiguous()
+
+    def wt(*shape):
+        return torch.randn(*shape, generator=g, **bf).mul_(w["std"])
+    weights = (wt(I, H), wt(I, H), wt(H, I), wt(e_loc, I, H), wt(e_loc, I, H), wt(e_loc, H, I))
+    return x, dy, topk.contiguous(), rw, weights
+
+
+def time_gemm_forms(dev, w, e_loc, sched, weights, rows_buf):
+    """Times single launches of the dominant kernel (tcgen05 grouped GEMM) on the layer's own shapes."""
+    import torch
+    from mok import _native as nat
+    H, I = w["H"], w["I"]
+    valid_rows = int((sched.peer_rank >= 0).sum().item())
+    padded_rows = int(sched.num_tokens.item())
+    rows_buf = min(rows_buf, (padded_rows + 255) // 256 * 256)
+    a_h = torch.randn(rows_buf, H, device=dev, dtype=torch.bfloat16)
+    a_i = torch.randn(rows_buf, I, device=dev, dtype=torch.bfloat16)
+    d_i = torch.empty(rows_buf, I, device=dev, dtype=torch.bfloat16)
+    d_w = torch.empty(e_loc, I, H, device=dev, dtype=torch.bfloat16)
+    st = nat.status_word(dev)
+    L = nat.lib()
+    tpe, nt = nat.ptr(sched.tokens_per_expert), nat.ptr(sched.num_tokens)
+
+    def fwd():
+        return L.mok_grouped_gemm_bf16(nat.ptr(a_h), nat.ptr(weights[3]), nat.ptr(d_i), tpe, nt, e_loc, rows_buf, I, H, 0,
+                                       nat.ptr(st), nat.stream_ptr(dev))
+
+    def dgrad():
+        return L.mok_grouped_gemm_bf16(nat.ptr(a_h), nat.ptr(weights[5]), nat.ptr(d_i), tpe, nt, e_loc, rows_buf, I, H, 1,
+                                       nat.ptr(st), nat.stream_ptr(dev))
+
+    def wgrad():
+        return L.mok_grouped_wgrad_bf16(nat.ptr(a_i), nat.ptr(a_h), nat.ptr(d_w), tpe, nt, e_loc, rows_buf, I, H,
+                                        nat.ptr(st), nat.stream_ptr(dev))
+    out = {}
+    rows_done = min(valid_rows, rows_buf)
+    for name, fn in (("fwd_gate", fwd), ("dgrad_down", dgrad), ("wgrad_gate", wgrad)):
+        for _ in range(2):
+            nat.check(fn(), name)
+        ev = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
+        reps = 5
+        torch.cuda.synchronize()
+        ev[0].record()
+        for _ in range(reps):
+            fn()
+        ev[1].record()
+        torch.cuda.synchronize()
+        ms = ev[0].elapsed_time(ev[1]) / reps
+        out[name] = {"ms": ms, "tflops": 2.0 * rows_done * H * I / (ms * 1e-3) / 1e12}
+    nat.check_status(dev)
+    return out, rows_done
+
+
+def run_gpu_arm(args, w):
+    import torch
+    import torch.distributed as dist
+    import mok
+    F = mok.functional
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} needs {args.gpus} ranks (torchrun), found WORLD_SIZE={world}")
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    os.environ.setdefault("MASTER_PORT", "29555")
+    dev = torch.device("cuda", local)
+    torch.cuda.set_device(dev)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+
+    T, H, E, I, K = w["T"], w["H"], w["E"], w["I"], w["K"]
+    e_loc = E // world
+    capacity_factor = max(2, -(-world // 2))
+    capacity = T * K * capacity_factor
+    # one window covers the expected rows (routes + per-expert padding) so backward never replays gate/up
+    expected = T * K + e_loc * 256
+    mb = min(capacity, -(-int(expected * 1.06) // 4096) * 4096)
+    if args.macrobatch:
+        mb = args.macrobatch
+    config = F.MoKConfig(minibatch_size=4096 if mb % 4096 == 0 else 256, macrobatch_size=mb)
+    x, dy, topk, rw, weights = make_gpu_inputs(w, e_loc, rank, dev)
+    ws = F.get_workspace(config, dist.group.WORLD, device=dev, num_local_tokens=T, hidden_size=H, topk=K)
+
+    def step(x_, dy_, topk_, rw_):
+        sched = F.build_schedule(ws, config, topk_, num_local_experts=e_loc)
+        out, ctx = F.forward(config, ws, sched, x_, rw_, *weights)
+        grads = F.backward(config, ws, sched, ctx, dy_, x_, rw_, *weights)
+        return sched, out, grads
+
+    def timed(fn, steps):
+        dist.barrier()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        dist.barrier()
+        ms = torch.tensor([e0.elapsed_time(e1)], device=dev, dtype=torch.float64)
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return ms.item() / steps
+
+    for _ in range(args.warmup):
+        out = step(x, dy, topk, rw)
+        del out
+    torch.cuda.synchronize()
+    mok.ops.check_status(dev)
+    sampler = ClockSampler(local)
+    sampler.start()
+    launches0 = mok.ops.lib().mok_launch_count()
+    ms_step = timed(lambda: step(x, dy, topk, rw), args.steps)
+    launches = (mok.ops.lib().mok_launch_count() - launches0) // args.steps
+    clocks = sampler.stop()
+    mok.ops.check_status(dev)
+
+    # end to end: host buffers in, results back to the host, every step
+    pin = lambda t: torch.empty(t.shape, dtype=t.dtype, pin_memory=True).copy_(t)  # noqa: E731
+    hx, hdy, htopk, hrw = pin(x), pin(dy), pin(topk), pin(rw)
+    dx_, ddy_, dtopk_, drw_ = torch.empty_like(x), torch.empty_like(dy), torch.empty_like(topk), torch.empty_like(rw)
+    hout, hdx, hdrw = pin(x), pin(x), pin(rw)
+
+    def e2e_step():
+        dx_.copy_(hx, non_blocking=True); ddy_.copy_(hdy, non_blocking=True)
+        dtopk_.copy_(htopk, non_blocking=True); drw_.copy_(hrw, non_blocking=True)
+        _, out, grads = step(dx_, ddy_, dtopk_, drw_)
+        hout.copy_(out, non_blocking=True); hdx.copy_(grads[0], non_blocking=True); hdrw.copy_(grads[1], non_blocking=True)
+    e2e_step()
+    ms_e2e = timed(e2e_step, max(1, min(args.steps, 3)))
+    h2d = sum(t.numel() * t.element_size() for t in (hx, hdy, htopk, hrw))
+    d2h = sum(t.numel() * t.element_size() for t in (hout, hdx, hdrw))
+
+    sched, out, grads = step(x, dy, topk, rw)
+    del out, grads
+    forms, rows_done = time_gemm_forms(dev, w, e_loc, sched, weights, mb)
+    if rank == 0:
+        peaks = measured_peaks()
+        tokens = T * world
+        fl = flops_per_token(w) * T            # per rank
+        dominant = forms["fwd_gate"]
+        line = {
+            "metric": "moe_layer_fwd_bwd_tokens_per_s", "value": tokens / (ms_step * 1e-3), "unit": "tokens/s",
+            "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": w["label"], "tokens_per_rank": T, "hidden": H, "experts": E, "intermediate": I, "topk": K,
+                       "shared_expert": True, "parallelism": f"ep{world}", "macrobatch_size": mb,
+                       "schedule_capacity": capacity, "l2_policy": "inputs_larger_than_L2"},
+            "tflops_per_gpu": fl / (ms_step * 1e-3) / 1e12,
+            "frac_of_bf16_peak_sustained": fl / (ms_step * 1e-3) / 1e12 / peaks["sustained"],
+            "roofline": {"bound": "tensor", "kernel": "grouped_gemm_kernel (forward gate form)", "achieved": dominant["tflops"],
+                         "peak": peaks["burst"], "unit": "TFLOP/s", "frac": dominant["tflops"] / peaks["burst"],
+                         "traffic": None, "peak_source": peaks["source"], "rows": rows_done, "forms": forms},
+            "e2e": {"value": tokens / (ms_e2e * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+            "gpu_launches": int(launches), "clocks": clocks,
+        }
+        if world == 1 and not args.no_cpu:
+            ct, ce = cpu_sample_size(w)
+            tps, sec, cores = cpu_sample(w, ct, ce, 1, 0)
+            line["cpu_baseline"] = {"value": tps, "unit": "tokens/s", "cores": cores, "kind": "port",
+                                    "sample": f"{ct} tokens, {ce} experts, H={H} I={I} top-{min(K, ce)}, one pass of the CPU oracle"}
+        print(json.dumps(line), flush=True)
+    F.clear_workspace_cache()
+    dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=("ours", "reference"))
+    ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
+    ap.add_argument("--macrobatch", type=int, default=0)
+    ap.add_argument("--no-cpu", action="store_true")
+    args = ap.parse_args()
+    w = WORKLOADS[args.workload]
+    if args.impl == "reference":
+        run_reference_arm(args, w)
+    else:
+        run_gpu_arm(args, w)
+
+
+if __name__ == "__main__":
+    main()

@@ -47,6 +47,9 @@ int mok_version(void);
 /* Last CUDA error string seen by this library on the calling thread ("" if none). */
 const char* mok_last_error(void);
 
+/* Kernels this library has launched in this process so far (all threads). */
+long long mok_launch_count(void);
+
 /* Bytes of int32 scratch `mok_schedule` needs for these sizes. */
 int64_t mok_schedule_scratch_bytes(int ep_size, int num_local_tokens, int topk, int num_local_experts);
 

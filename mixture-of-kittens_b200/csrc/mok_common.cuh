@@ -27,7 +27,10 @@ int fail_cuda(const char* what, cudaError_t err);
     do {                                                                 \
         cudaError_t _e = cudaGetLastError();                             \
         if (_e != cudaSuccess) return ::mok::fail_cuda(name, _e);        \
+        ::mok::note_launch();                                            \
     } while (0)
+
+void note_launch();   // counts kernel launches of this library (mok_launch_count)
 
 int sm_count();   // multiprocessors of the current device (cached per device)
 

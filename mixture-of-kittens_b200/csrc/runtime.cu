@@ -1,4 +1,5 @@
 // Library-wide host helpers: version, last-error string, cached device properties.
+#include <atomic>
 #include <stdio.h>
 #include <string.h>
 
@@ -7,7 +8,10 @@
 namespace mok {
 namespace {
 thread_local char g_last_error[512] = "";
+std::atomic<long long> g_launches{0};
 }
+
+void note_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
 
 void set_last_error(const char* what, cudaError_t err) {
     snprintf(g_last_error, sizeof(g_last_error), "%s: %s", what, cudaGetErrorString(err));
@@ -34,3 +38,5 @@ int sm_count() {
 extern "C" int mok_version(void) { return 100; }
 
 extern "C" const char* mok_last_error(void) { return mok::g_last_error; }
+
+extern "C" long long mok_launch_count(void) { return mok::g_launches.load(); }

@@ -53,6 +53,7 @@ def lib() -> ctypes.CDLL:
         L = ctypes.CDLL(_LIB_PATH)
         L.mok_version.restype = c_int
         L.mok_last_error.restype = c_char_p
+        L.mok_launch_count.restype = ctypes.c_longlong
         L.mok_schedule_scratch_bytes.restype = c_int64
         L.mok_schedule_scratch_bytes.argtypes = [c_int, c_int, c_int, c_int]
         L.mok_schedule.argtypes = [c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
