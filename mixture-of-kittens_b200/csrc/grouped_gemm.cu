@@ -1,12 +1,16 @@
 // Grouped bf16 GEMM for sm_100a: tcgen05.mma with fp32 accumulators in tensor memory, operands staged in
-// shared memory by TMA (128-byte swizzle), persistent CTAs over a static tile list.
+// shared memory by TMA (128-byte swizzle), persistent CTA pairs over a static tile list.
 //
+// Two CTAs (a cluster of 2, "cta_group::2") share one 256 x 256 output tile: each CTA stages its own 128 rows
+// of A and its own 128-column half of B (plain TMA loads, 32 KB per K step and CTA instead of 48 KB for a
+// 128 x 256 single-CTA tile), the leader CTA issues one 256-row MMA per 16-wide K slice that reads both CTAs'
+// shared memory, and each CTA owns the 128 x 256 fp32 accumulator of its rows in its tensor memory.
 // One CTA = 6 warps:
-//   warp 0        TMA producer (one elected lane)
-//   warp 1        MMA issuer (one elected lane); owns the tensor-memory allocation
+//   warp 0        TMA producer (one elected lane); credits the leader's "full" barrier
+//   warp 1        MMA issuer (leader CTA only, one elected lane); owns the tensor-memory allocation
 //   warps 2..5    epilogue: tensor memory -> registers -> bf16 -> global (each warp owns 32 accumulator lanes)
-// Tile 128 x 256, K step 64, 4-stage operand ring (48 KB per stage), two 256-column accumulators in
-// tensor memory so the epilogue of tile i overlaps the main loop of tile i+1.
+// K step 64, 6-stage operand ring, two 256-column accumulators so the epilogue of tile i overlaps the main
+// loop of tile i+1.
 //
 // Three forms (the roles the reference gives its grouped GEMM, csrc/megakernel/grouped_gemm.cuh):
 //   rows / B [E,N,K]   D[r,:] = A[r,:] B[e]^T          forward gate, up, down            (A, B K-major)
@@ -18,12 +22,14 @@
 namespace mok {
 namespace {
 
-constexpr int BM = 128;
+constexpr int BM = 256;                              // tile rows of the CTA pair
+constexpr int BM_CTA = 128;                          // rows each CTA stages and accumulates
 constexpr int BN = 256;
+constexpr int BN_CTA = 128;                          // B columns each CTA stages
 constexpr int BK = 64;
-constexpr int STAGES = 4;
-constexpr int A_TILE_BYTES = BM * BK * 2;            // 16 KB
-constexpr int B_TILE_BYTES = BN * BK * 2;            // 32 KB
+constexpr int STAGES = 6;
+constexpr int A_TILE_BYTES = BM_CTA * BK * 2;        // 16 KB
+constexpr int B_TILE_BYTES = BN_CTA * BK * 2;        // 16 KB
 constexpr int STAGE_BYTES = A_TILE_BYTES + B_TILE_BYTES;
 constexpr int CHUNK_BYTES = 64 * BK * 2;             // one 64(MN) x 64(K) block of an MN-major operand: 8 KB
 constexpr int NUM_THREADS = 192;
@@ -38,7 +44,7 @@ struct KernelParams {
     int dense_rows;
     int row_begin, row_end;
     int n_blocks;     // rows: N / 256 per output set; wgrad: N / 256
-    int m_blocks_w;   // wgrad: M / 128
+    int m_blocks_w;   // wgrad: M / 256
     int k_blocks;     // rows: K / 64 per operand set
     int n_sets;       // rows: output sets sharing A (1 or 2)
     int k_sets;       // rows: operand sets accumulated into one output (1 or 2)
@@ -59,14 +65,13 @@ struct Tile {
 };
 
 struct SharedLayout {
-    // dynamic shared memory, 1024-byte aligned base:
-    //   [0, STAGES*STAGE_BYTES)  operand ring
-    //   then barriers, bookkeeping, and the expert row prefix
+    // dynamic shared memory, 1024-byte aligned base (identical in both CTAs of a pair):
+    //   [0, STAGES*STAGE_BYTES)  operand ring, then barriers, bookkeeping, and the expert row prefix
     static constexpr int kBarrierOffset = STAGES * STAGE_BYTES;
-    static constexpr int kFull = kBarrierOffset;                  // STAGES x 8 B
+    static constexpr int kFull = kBarrierOffset;                  // STAGES x 8 B (leader's are used)
     static constexpr int kEmpty = kFull + 8 * STAGES;             // STAGES x 8 B
     static constexpr int kTmemFull = kEmpty + 8 * STAGES;         // 2 x 8 B
-    static constexpr int kTmemEmpty = kTmemFull + 16;             // 2 x 8 B
+    static constexpr int kTmemEmpty = kTmemFull + 16;             // 2 x 8 B (leader's are used)
     static constexpr int kTmemPtr = kTmemEmpty + 16;              // 4 B
     static constexpr int kAbort = kTmemPtr + 4;                   // 4 B
     static constexpr int kCum = kAbort + 4 + 8;                   // (E + 1) x 4 B
@@ -156,16 +161,19 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_const
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
+    const int cta_rank = static_cast<int>(cluster_cta_rank());   // 0 = leader of the pair
+    const int pair = blockIdx.x >> 1;
+    const int num_pairs = gridDim.x >> 1;
 
     // ---- set-up ---------------------------------------------------------------------------------------
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
-            mbar_init(bar_full + 8 * s, 1);
-            mbar_init(bar_empty + 8 * s, 1);
+            mbar_init(bar_full + 8 * s, 1);      // leader: one arrive.expect_tx covering both CTAs' bytes
+            mbar_init(bar_empty + 8 * s, 1);     // one commit per use, delivered to both CTAs
         }
         for (int s = 0; s < 2; ++s) {
             mbar_init(bar_tmem_full + 8 * s, 1);
-            mbar_init(bar_tmem_empty + 8 * s, 4);
+            mbar_init(bar_tmem_empty + 8 * s, 8);   // leader: four epilogue warps of each CTA
         }
         *abort_flag = 0;
         mbar_fence_init();
@@ -175,8 +183,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_const
         if (p.k_sets > 1 || p.n_sets > 1) tma_prefetch_desc(&tmB1);
     }
     if (warp == 1) {
-        tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_ptr_slot)), TMEM_COLS);
-        tmem_relinquish();
+        tmem_alloc_pair(smem_u32(const_cast<uint32_t*>(tmem_ptr_slot)), TMEM_COLS);
+        tmem_relinquish_pair();
     }
     if (warp == 2) {   // inclusive prefix of the per-expert row counts -> cum[0..E]
         if (p.tokens_per_expert == nullptr) {
@@ -199,6 +207,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_const
     }
     tc_fence_before_sync();
     __syncthreads();
+    cluster_sync_all();     // both CTAs' barriers exist before either one signals the other
     tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_ptr_slot;
 
@@ -212,41 +221,43 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_const
     constexpr uint32_t kIdesc = umma_idesc_bf16(BM, BN, A_MN, B_MN);
 
     if (warp == 0) {
-        // ---- TMA producer ---------------------------------------------------------------------------
+        // ---- TMA producer (both CTAs) -----------------------------------------------------------------
         int stage = 0;
         uint32_t phase = 0;
         bool ok = true;
-        for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+        for (int t = pair; t < total_tiles && ok; t += num_pairs) {
             Tile tile;
             if (!decode_tile<MODE>(p, cum, lo, hi, t, tile)) continue;
             for (int kb = 0; kb < tile.k_blocks; ++kb) {
                 ok = mbar_wait(bar_empty + 8 * stage, phase ^ 1u, abort_flag, p.status);
                 if (!ok) break;
                 if (lane == 0) {
-                    const uint32_t full = bar_full + 8 * stage;
+                    const uint32_t full_local = bar_full + 8 * stage;
+                    const uint32_t full = full_local & kPairLeaderMask;   // the leader's barrier collects all bytes
                     const uint32_t a_dst = smem_base + stage * STAGE_BYTES;
                     const uint32_t b_dst = a_dst + A_TILE_BYTES;
-                    mbar_expect_tx(full, STAGE_BYTES);
+                    if (cta_rank == 0) mbar_expect_tx(full_local, 2 * STAGE_BYTES);
                     if (MODE == MODE_ROWS) {
                         const int kset = kb >= p.k_blocks ? 1 : 0;
                         const int kk = (kb - kset * p.k_blocks) * BK;
-                        tma_load_4d(a_dst, kset ? &tmA1 : &tmA0, full, kk, tile.row0 - p.row_begin, 0, 0);
+                        tma_load_4d_pair(a_dst, kset ? &tmA1 : &tmA0, full, kk, tile.row0 - p.row_begin + cta_rank * BM_CTA, 0, 0);
                         const CUtensorMap* bmap = (kset || tile.set) ? &tmB1 : &tmB0;
+                        const int n_cta = tile.n0 + cta_rank * BN_CTA;
                         if (!B_MN) {
-                            tma_load_4d(b_dst, bmap, full, kk, tile.n0, tile.expert, 0);
+                            tma_load_4d_pair(b_dst, bmap, full, kk, n_cta, tile.expert, 0);
                         } else {
 #pragma unroll
-                            for (int c = 0; c < BN / 64; ++c)
-                                tma_load_4d(b_dst + c * CHUNK_BYTES, bmap, full, tile.n0 + c * 64, kk, tile.expert, 0);
+                            for (int c = 0; c < BN_CTA / 64; ++c)
+                                tma_load_4d_pair(b_dst + c * CHUNK_BYTES, bmap, full, n_cta + c * 64, kk, tile.expert, 0);
                         }
                     } else {
                         const int krow = tile.row0 + kb * BK - p.row_begin;
 #pragma unroll
-                        for (int c = 0; c < BM / 64; ++c)
-                            tma_load_4d(a_dst + c * CHUNK_BYTES, &tmA0, full, tile.m0 + c * 64, krow, 0, 0);
+                        for (int c = 0; c < BM_CTA / 64; ++c)
+                            tma_load_4d_pair(a_dst + c * CHUNK_BYTES, &tmA0, full, tile.m0 + cta_rank * BM_CTA + c * 64, krow, 0, 0);
 #pragma unroll
-                        for (int c = 0; c < BN / 64; ++c)
-                            tma_load_4d(b_dst + c * CHUNK_BYTES, &tmB0, full, tile.n0 + c * 64, krow, 0, 0);
+                        for (int c = 0; c < BN_CTA / 64; ++c)
+                            tma_load_4d_pair(b_dst + c * CHUNK_BYTES, &tmB0, full, tile.n0 + cta_rank * BN_CTA + c * 64, krow, 0, 0);
                     }
                 }
                 __syncwarp();
@@ -254,51 +265,53 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_const
             }
         }
     } else if (warp == 1) {
-        // ---- MMA issuer -----------------------------------------------------------------------------
-        int stage = 0;
-        uint32_t phase = 0;
-        int iter = 0;
-        bool ok = true;
-        // descriptor steps per 16-wide K slice (units of 16 bytes): 32 B inside a K-major swizzle row,
-        // two 8-row groups (2 KB) of an MN-major tile
-        constexpr uint32_t kAStep = A_MN ? 128u : 2u;
-        constexpr uint32_t kBStep = B_MN ? 128u : 2u;
-        for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
-            Tile tile;
-            if (!decode_tile<MODE>(p, cum, lo, hi, t, tile)) continue;
-            const int acc = iter & 1;
-            const uint32_t acc_phase = (iter >> 1) & 1u;
-            ok = mbar_wait(bar_tmem_empty + 8 * acc, acc_phase ^ 1u, abort_flag, p.status);
-            if (!ok) break;
-            tc_fence_after_sync();
-            const uint32_t d_tmem = tmem_base + acc * BN;
-            for (int kb = 0; kb < tile.k_blocks; ++kb) {
-                ok = mbar_wait(bar_full + 8 * stage, phase, abort_flag, p.status);
+        // ---- MMA issuer (leader CTA only) ----------------------------------------------------------------
+        if (cta_rank == 0) {
+            int stage = 0;
+            uint32_t phase = 0;
+            int iter = 0;
+            bool ok = true;
+            // descriptor steps per 16-wide K slice (units of 16 bytes): 32 B inside a K-major swizzle row,
+            // two 8-row groups (2 KB) of an MN-major tile
+            constexpr uint32_t kAStep = A_MN ? 128u : 2u;
+            constexpr uint32_t kBStep = B_MN ? 128u : 2u;
+            for (int t = pair; t < total_tiles && ok; t += num_pairs) {
+                Tile tile;
+                if (!decode_tile<MODE>(p, cum, lo, hi, t, tile)) continue;
+                const int acc = iter & 1;
+                const uint32_t acc_phase = (iter >> 1) & 1u;
+                ok = mbar_wait(bar_tmem_empty + 8 * acc, acc_phase ^ 1u, abort_flag, p.status);
                 if (!ok) break;
                 tc_fence_after_sync();
-                if (lane == 0) {
-                    const uint32_t a_addr = smem_base + stage * STAGE_BYTES;
-                    const uint32_t b_addr = a_addr + A_TILE_BYTES;
-                    const uint64_t a_desc = A_MN ? umma_smem_desc(a_addr, CHUNK_BYTES, 1024) : umma_smem_desc(a_addr, 16, 1024);
-                    const uint64_t b_desc = B_MN ? umma_smem_desc(b_addr, CHUNK_BYTES, 1024) : umma_smem_desc(b_addr, 16, 1024);
+                const uint32_t d_tmem = tmem_base + acc * BN;
+                for (int kb = 0; kb < tile.k_blocks; ++kb) {
+                    ok = mbar_wait(bar_full + 8 * stage, phase, abort_flag, p.status);
+                    if (!ok) break;
+                    tc_fence_after_sync();
+                    if (lane == 0) {
+                        const uint32_t a_addr = smem_base + stage * STAGE_BYTES;
+                        const uint32_t b_addr = a_addr + A_TILE_BYTES;
+                        const uint64_t a_desc = A_MN ? umma_smem_desc(a_addr, CHUNK_BYTES, 1024) : umma_smem_desc(a_addr, 16, 1024);
+                        const uint64_t b_desc = B_MN ? umma_smem_desc(b_addr, CHUNK_BYTES, 1024) : umma_smem_desc(b_addr, 16, 1024);
 #pragma unroll
-                    for (int k = 0; k < BK / 16; ++k)
-                        umma_bf16(d_tmem, a_desc + k * kAStep, b_desc + k * kBStep, kIdesc, (kb | k) != 0 ? 1u : 0u);
-                    umma_commit(bar_empty + 8 * stage);                       // frees the operand stage
-                    if (kb == tile.k_blocks - 1) umma_commit(bar_tmem_full + 8 * acc);   // accumulator complete
+                        for (int k = 0; k < BK / 16; ++k)
+                            umma_bf16_pair(d_tmem, a_desc + k * kAStep, b_desc + k * kBStep, kIdesc, (kb | k) != 0 ? 1u : 0u);
+                        umma_commit_pair(bar_empty + 8 * stage);                            // frees the stage in both CTAs
+                        if (kb == tile.k_blocks - 1) umma_commit_pair(bar_tmem_full + 8 * acc);   // accumulators complete
+                    }
+                    __syncwarp();
+                    if (++stage == STAGES) { stage = 0; phase ^= 1u; }
                 }
-                __syncwarp();
-                if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+                ++iter;
             }
-            ++iter;
         }
     } else {
-        // ---- epilogue -------------------------------------------------------------------------------
+        // ---- epilogue (both CTAs, each for its own 128 rows) ----------------------------------------------
         const int quarter = warp & 3;                 // tensor-memory lanes [32*quarter, 32*quarter + 32)
-        const int row_in_tile = quarter * 32 + lane;
+        const int row_in_tile = cta_rank * BM_CTA + quarter * 32 + lane;
         int iter = 0;
         bool ok = true;
-        for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+        for (int t = pair; t < total_tiles && ok; t += num_pairs) {
             Tile tile;
             if (!decode_tile<MODE>(p, cum, lo, hi, t, tile)) continue;
             const int acc = iter & 1;
@@ -322,7 +335,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_const
             }
             tc_fence_before_sync();
             __syncwarp();
-            if (lane == 0) mbar_arrive(bar_tmem_empty + 8 * acc);
+            if (lane == 0) mbar_arrive_leader(bar_tmem_empty + 8 * acc);
             ++iter;
         }
     }
@@ -333,9 +346,10 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_const
     }
     tc_fence_before_sync();
     __syncthreads();
+    cluster_sync_all();   // the peer's shared memory and barriers stay valid until both CTAs are done
     if (warp == 1) {
         tc_fence_after_sync();
-        tmem_dealloc(tmem_base, TMEM_COLS);
+        tmem_dealloc_pair(tmem_base, TMEM_COLS);
     }
 }
 
@@ -383,32 +397,55 @@ size_t smem_bytes(int num_experts) {
     return 1024 + SharedLayout::kCum + 4 * (static_cast<size_t>(num_experts) + 2);
 }
 
+constexpr int kMaxDynamicSmem = 232448 - 1024;
+
 template <int MODE, bool B_MN>
 int launch(const CUtensorMap& a0, const CUtensorMap& b0, const CUtensorMap& a1, const CUtensorMap& b1,
            const KernelParams& kp, int max_tiles, cudaStream_t stream) {
     auto kernel = grouped_gemm_kernel<MODE, B_MN>;
     const size_t smem = smem_bytes(kp.num_experts);
-    static size_t configured[16] = {0};   // per device
+    static int max_pairs[16] = {0};   // per device: CTA pairs that can be resident at once
     int dev = 0;
     MOK_CUDA_CHECK(cudaGetDevice(&dev));
-    if (dev < 16 && configured[dev] < smem) {
-        MOK_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 232448 - 1024));
-        configured[dev] = 232448;
+    if (dev < 0 || dev >= 16) return MOK_ERR_UNSUPPORTED;
+
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cudaLaunchConfig_t cfg = {};
+    cfg.blockDim = dim3(NUM_THREADS);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+
+    if (max_pairs[dev] == 0) {
+        MOK_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxDynamicSmem));
+        cfg.gridDim = dim3(2 * sm_count());
+        cfg.dynamicSmemBytes = kMaxDynamicSmem;
+        int clusters = 0;
+        MOK_CUDA_CHECK(cudaOccupancyMaxActiveClusters(&clusters, kernel, &cfg));
+        cfg.dynamicSmemBytes = smem;
+        max_pairs[dev] = clusters > 0 ? clusters : sm_count() / 2;
     }
-    int grid = sm_count();
-    if (max_tiles < grid) grid = max_tiles;
-    if (grid <= 0) return MOK_OK;
-    kernel<<<grid, NUM_THREADS, smem, stream>>>(a0, b0, a1, b1, kp);
+    int pairs = max_pairs[dev];
+    if (max_tiles < pairs) pairs = max_tiles;
+    if (pairs <= 0) return MOK_OK;
+    cfg.gridDim = dim3(2 * pairs);
+    cudaError_t err = cudaLaunchKernelEx(&cfg, kernel, a0, b0, a1, b1, kp);
+    if (err != cudaSuccess) return fail_cuda("grouped_gemm_kernel launch", err);
     MOK_LAUNCH_CHECK("grouped_gemm_kernel");
     return MOK_OK;
 }
 
 int check_problem(const GemmProblem& pb) {
     if (pb.num_experts < 1 || pb.num_experts > MOK_MAX_LOCAL_EXPERTS) return MOK_ERR_TOO_LARGE;
-    if (pb.row_begin < 0 || pb.row_end < pb.row_begin || (pb.row_begin % 256) != 0 || (pb.row_end % 128) != 0)
+    if (pb.row_begin < 0 || pb.row_end < pb.row_begin || (pb.row_begin % BM) != 0 || (pb.row_end % BM) != 0)
         return MOK_ERR_INVALID_ARGUMENT;
     if (pb.buffer_rows <= 0) return MOK_ERR_INVALID_ARGUMENT;
-    if (pb.tokens_per_expert == nullptr && (pb.num_experts != 1 || pb.dense_rows % 128 != 0)) return MOK_ERR_INVALID_ARGUMENT;
+    if (pb.tokens_per_expert == nullptr && (pb.num_experts != 1 || pb.dense_rows % BM != 0)) return MOK_ERR_INVALID_ARGUMENT;
     if (pb.tokens_per_expert != nullptr && pb.num_tokens == nullptr) return MOK_ERR_INVALID_ARGUMENT;
     return MOK_OK;
 }
@@ -436,10 +473,10 @@ int launch_rows_gemm(const GemmProblem& pb, const void* A, int K, const void* B0
     if (K <= 0 || N <= 0 || K % BK != 0 || N % BN != 0) return MOK_ERR_INVALID_ARGUMENT;
     const int n_sets = (B1 != nullptr) ? 2 : 1;
     CUtensorMap a0, b0, b1;
-    if ((rc = make_map(&a0, A, K, pb.buffer_rows, 1, BK, BM)) != MOK_OK) return rc;
+    if ((rc = make_map(&a0, A, K, pb.buffer_rows, 1, BK, BM_CTA)) != MOK_OK) return rc;
     if (!b_is_kn) {
-        if ((rc = make_map(&b0, B0, K, N, pb.num_experts, BK, BN)) != MOK_OK) return rc;
-        if ((rc = make_map(&b1, n_sets == 2 ? B1 : B0, K, N, pb.num_experts, BK, BN)) != MOK_OK) return rc;
+        if ((rc = make_map(&b0, B0, K, N, pb.num_experts, BK, BN_CTA)) != MOK_OK) return rc;
+        if ((rc = make_map(&b1, n_sets == 2 ? B1 : B0, K, N, pb.num_experts, BK, BN_CTA)) != MOK_OK) return rc;
     } else {
         if ((rc = make_map(&b0, B0, N, K, pb.num_experts, 64, BK)) != MOK_OK) return rc;
         if ((rc = make_map(&b1, n_sets == 2 ? B1 : B0, N, K, pb.num_experts, 64, BK)) != MOK_OK) return rc;
@@ -463,8 +500,8 @@ int launch_rows_gemm_dual(const GemmProblem& pb, const void* A0, const void* A1,
     if (rc != MOK_OK) return rc;
     if (K <= 0 || N <= 0 || K % BK != 0 || N % BN != 0) return MOK_ERR_INVALID_ARGUMENT;
     CUtensorMap a0, a1, b0, b1;
-    if ((rc = make_map(&a0, A0, K, pb.buffer_rows, 1, BK, BM)) != MOK_OK) return rc;
-    if ((rc = make_map(&a1, A1, K, pb.buffer_rows, 1, BK, BM)) != MOK_OK) return rc;
+    if ((rc = make_map(&a0, A0, K, pb.buffer_rows, 1, BK, BM_CTA)) != MOK_OK) return rc;
+    if ((rc = make_map(&a1, A1, K, pb.buffer_rows, 1, BK, BM_CTA)) != MOK_OK) return rc;
     if ((rc = make_map(&b0, B0, N, K, pb.num_experts, 64, BK)) != MOK_OK) return rc;
     if ((rc = make_map(&b1, B1, N, K, pb.num_experts, 64, BK)) != MOK_OK) return rc;
     KernelParams kp = base_params(pb);
@@ -499,10 +536,8 @@ int launch_wgrad_gemm(const GemmProblem& pb, const void* A, int M, const void* B
 // ---------------------------------------------------------------------------------------------------------
 // C ABI: single launches, for tests and profiling
 // ---------------------------------------------------------------------------------------------------------
-extern "C" int mok_grouped_gemm_bf16(const void* A, const void* B, void* D, const int32_t* tokens_per_expert,
-                                     const int32_t* num_tokens, int num_experts, int rows, int N, int K, int b_is_kn,
-                                     uint32_t* status, mok_stream_t stream) {
-    if (A == nullptr || B == nullptr || D == nullptr || rows <= 0 || rows % 128 != 0) return MOK_ERR_INVALID_ARGUMENT;
+static mok::GemmProblem single_launch_problem(const int32_t* tokens_per_expert, const int32_t* num_tokens, int num_experts,
+                                              int rows, uint32_t* status) {
     mok::GemmProblem pb;
     pb.tokens_per_expert = tokens_per_expert;
     pb.num_tokens = num_tokens;
@@ -512,21 +547,21 @@ extern "C" int mok_grouped_gemm_bf16(const void* A, const void* B, void* D, cons
     pb.row_end = rows;
     pb.buffer_rows = rows;
     pb.status = status;
+    return pb;
+}
+
+extern "C" int mok_grouped_gemm_bf16(const void* A, const void* B, void* D, const int32_t* tokens_per_expert,
+                                     const int32_t* num_tokens, int num_experts, int rows, int N, int K, int b_is_kn,
+                                     uint32_t* status, mok_stream_t stream) {
+    if (A == nullptr || B == nullptr || D == nullptr || rows <= 0 || rows % 256 != 0) return MOK_ERR_INVALID_ARGUMENT;
+    const mok::GemmProblem pb = single_launch_problem(tokens_per_expert, num_tokens, num_experts, rows, status);
     return mok::launch_rows_gemm(pb, A, K, B, nullptr, D, nullptr, N, b_is_kn != 0, reinterpret_cast<cudaStream_t>(stream));
 }
 
 extern "C" int mok_grouped_wgrad_bf16(const void* A, const void* B, void* D, const int32_t* tokens_per_expert,
                                       const int32_t* num_tokens, int num_experts, int rows, int M, int N,
                                       uint32_t* status, mok_stream_t stream) {
-    if (A == nullptr || B == nullptr || D == nullptr || rows <= 0 || rows % 128 != 0) return MOK_ERR_INVALID_ARGUMENT;
-    mok::GemmProblem pb;
-    pb.tokens_per_expert = tokens_per_expert;
-    pb.num_tokens = num_tokens;
-    pb.num_experts = tokens_per_expert ? num_experts : 1;
-    pb.dense_rows = tokens_per_expert ? 0 : rows;
-    pb.row_begin = 0;
-    pb.row_end = rows;
-    pb.buffer_rows = rows;
-    pb.status = status;
+    if (A == nullptr || B == nullptr || D == nullptr || rows <= 0 || rows % 256 != 0) return MOK_ERR_INVALID_ARGUMENT;
+    const mok::GemmProblem pb = single_launch_problem(tokens_per_expert, num_tokens, num_experts, rows, status);
     return mok::launch_wgrad_gemm(pb, A, M, B, N, D, reinterpret_cast<cudaStream_t>(stream));
 }
