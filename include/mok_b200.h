@@ -71,6 +71,23 @@ int mok_schedule(const int32_t* topk_all, int ep_size, int num_local_tokens, int
                  int32_t* tokens_per_expert, int32_t* scratch, uint32_t* status, mok_stream_t stream);
 
 /*
+ * Same result as mok_schedule, for callers that must not allocate device memory around the call: a serving
+ * process whose memory pool is frozen after start-up, or a plugin running under another framework's allocator
+ * lock.  It has no counterpart in the reference project.  The scratch is a fixed array inside the library (MOK_SCHEDULE_STATIC_SCRATCH_BYTES on every
+ * GPU that loads the library, held until process exit), so:
+ *   - sizes with mok_schedule_scratch_bytes() above that limit are rejected with MOK_ERR_TOO_LARGE;
+ *   - the first call on each device looks up the array's device address; make that first call outside any
+ *     stream capture;
+ *   - all calls on one GPU share the array: two calls that may overlap on the GPU (different streams) race.
+ * Neither this function nor anything it launches calls cudaMalloc / cudaFree.
+ */
+#define MOK_SCHEDULE_STATIC_SCRATCH_BYTES (4 * 1024 * 1024)
+int mok_schedule_static(const int32_t* topk_all, int ep_size, int num_local_tokens, int topk,
+                        int num_local_experts, int schedule_capacity, int rank,
+                        int32_t* peer_rank, int32_t* peer_token_idx, int32_t* num_tokens,
+                        int32_t* tokens_per_expert, uint32_t* status, mok_stream_t stream);
+
+/*
  * Copies this rank's int32 routes [T*K] into slot `rank` of the [ep, T, K] buffer of every peer.
  * Replaces: all_gather_top_experts_kernel, csrc/utils.cuh:191-227 (op mok/ops.py:6-61).  Peers are
  * addressed one by one through `peer_buffers` (unicast stores); no multicast object is needed.

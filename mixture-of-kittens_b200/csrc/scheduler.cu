@@ -226,3 +226,60 @@ extern "C" int mok_schedule(const int32_t* topk_all, int ep_size, int num_local_
     MOK_LAUNCH_CHECK("scatter_kernel");
     return MOK_OK;
 }
+
+// ---------------------------------------------------------------------------------------------------------
+// Schedule builder for callers that cannot allocate device memory
+// ---------------------------------------------------------------------------------------------------------
+// Some hosts of this library may not call cudaMalloc at the point where they need a schedule: a serving loop
+// whose memory pool is frozen after start-up (an allocation there would fragment or overrun a budget that was
+// sized once), or a plugin that runs while another framework holds its allocator lock (a nested allocation would
+// deadlock or bypass that framework's accounting).  For them the scheduler's scratch lives in this fixed array.
+// Every GPU that loads the library holds its own copy until the process exits.
+namespace mok {
+namespace {
+constexpr long long kStaticScratchInts = MOK_SCHEDULE_STATIC_SCRATCH_BYTES / 4;
+static __device__ __align__(256) int32_t g_schedule_scratch[kStaticScratchInts];
+
+// The array's name is only a host-side handle; kernels need its device address, which differs per device.
+int32_t* static_scratch_address(int device, int* rc) {
+    static int32_t* cached[16] = {nullptr};
+    *rc = MOK_OK;
+    if (device < 0 || device >= 16) {
+        *rc = MOK_ERR_UNSUPPORTED;
+        return nullptr;
+    }
+    if (cached[device] == nullptr) {
+        void* p = nullptr;
+        const cudaError_t err = cudaGetSymbolAddress(&p, g_schedule_scratch);   // resolves for the current device
+        if (err != cudaSuccess || p == nullptr) {
+            *rc = fail_cuda("cudaGetSymbolAddress(schedule scratch)", err);
+            return nullptr;
+        }
+        cached[device] = static_cast<int32_t*>(p);
+    }
+    return cached[device];
+}
+}  // namespace
+}  // namespace mok
+
+extern "C" int mok_schedule_static(const int32_t* topk_all, int ep_size, int num_local_tokens, int topk,
+                                   int num_local_experts, int schedule_capacity, int rank, int32_t* peer_rank,
+                                   int32_t* peer_token_idx, int32_t* num_tokens, int32_t* tokens_per_expert,
+                                   uint32_t* status, mok_stream_t stream) {
+    if (ep_size < 1 || num_local_tokens <= 0 || topk <= 0 || num_local_experts <= 0) return MOK_ERR_INVALID_ARGUMENT;
+    const int64_t need = mok_schedule_scratch_bytes(ep_size, num_local_tokens, topk, num_local_experts);
+    if (need > MOK_SCHEDULE_STATIC_SCRATCH_BYTES) {
+        mok::set_last_error("mok_schedule_static: sizes need more scratch than MOK_SCHEDULE_STATIC_SCRATCH_BYTES; "
+                            "use mok_schedule with caller-provided scratch", cudaErrorInvalidValue);
+        return MOK_ERR_TOO_LARGE;
+    }
+    int device = 0;
+    MOK_CUDA_CHECK(cudaGetDevice(&device));
+    int rc = MOK_OK;
+    int32_t* scratch = mok::static_scratch_address(device, &rc);
+    if (scratch == nullptr) return rc;
+    // Every scratch word the kernels read is written earlier in the same call, so stale contents of the previous
+    // call need no clearing.
+    return mok_schedule(topk_all, ep_size, num_local_tokens, topk, num_local_experts, schedule_capacity, rank, peer_rank,
+                        peer_token_idx, num_tokens, tokens_per_expert, scratch, status, stream);
+}

@@ -58,6 +58,9 @@ def lib() -> ctypes.CDLL:
         L.mok_schedule_scratch_bytes.argtypes = [c_int, c_int, c_int, c_int]
         L.mok_schedule.argtypes = [c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
                                    c_void_p, c_void_p, c_void_p]
+        L.mok_schedule_static.argtypes = [c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p,
+                                          c_void_p, c_void_p, c_void_p]
+        L.mok_schedule_static.restype = c_int
         L.mok_all_gather_top_experts.argtypes = [c_void_p, c_int64, POINTER(c_uint64), c_int, c_int, c_void_p]
         L.mok_barrier_all.argtypes = [c_void_p, POINTER(c_uint64), c_int, c_void_p, c_void_p, c_int, c_void_p]
         L.mok_fwd_epilogue.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_void_p]
