@@ -320,8 +320,35 @@ def run_gpu_arm(args, w):
     dist.destroy_process_group()
 
 
+def run_gemm_only(args, w):
+    """Small stand-alone case of the dominant kernel for profiling: `--gemm-only ROWS` schedule rows spread evenly
+    over `--gemm-experts` experts of the workload's H and I (a few hundred MB: larger than L2, quick to capture)."""
+    import types
+    import torch
+    import mok  # noqa: F401
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    e, rows = args.gemm_experts, args.gemm_only
+    per = rows // e // 256 * 256
+    rows = per * e
+    H, I = w["H"], w["I"]
+    sched = types.SimpleNamespace(
+        peer_rank=torch.zeros(rows, dtype=torch.int32, device=dev),
+        num_tokens=torch.tensor([rows], dtype=torch.int32, device=dev),
+        tokens_per_expert=torch.full((e,), per, dtype=torch.int32, device=dev))
+    g = torch.Generator(device=dev).manual_seed(0)
+    wt = lambda *s: torch.randn(*s, generator=g, device=dev, dtype=torch.bfloat16).mul_(w["std"])  # noqa: E731
+    weights = (None, None, None, wt(e, I, H), None, wt(e, H, I))
+    forms, rows_done = time_gemm_forms(dev, w, e, sched, weights, rows)
+    peaks = measured_peaks()
+    print(json.dumps({"mode": "gemm-only", "rows": rows_done, "experts": e, "hidden": H, "intermediate": I, "forms": forms,
+                      "peak_burst_tflops": peaks["burst"], "peak_source": peaks["source"]}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
+    ap.add_argument("--gemm-only", type=int, default=0, help="profile helper: time only the GEMM forms on this many rows")
+    ap.add_argument("--gemm-experts", type=int, default=16)
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
@@ -331,7 +358,9 @@ def main():
     ap.add_argument("--no-cpu", action="store_true")
     args = ap.parse_args()
     w = WORKLOADS[args.workload]
-    if args.impl == "reference":
+    if args.gemm_only:
+        run_gemm_only(args, w)
+    elif args.impl == "reference":
         run_reference_arm(args, w)
     else:
         run_gpu_arm(args, w)
