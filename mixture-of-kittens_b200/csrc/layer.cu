@@ -1,10 +1,21 @@
 // Fused-layer entry points: the launch sequences for the BF16 forward, context recomputation and backward of
-// the expert-parallel MoE layer.  Everything is enqueued on the caller's stream; no host synchronisation.
+// the expert-parallel MoE layer.  Everything is enqueued from the caller's stream; no host synchronisation.
 //
 // Routed activations live in buffers of `macrobatch_size` rows.  Schedule rows are processed in windows of that
 // size ("macrobatches"); forward walks the windows last to first so that window 0's activations are what the
 // buffers hold afterwards, and backward recomputes gate / up / hidden for windows >= 1 before using them
 // (reference: csrc/megakernel/forward.cuh:117-129,202-209 and backward.cuh:147-176,296-329).
+//
+// Overlap of NVLink traffic with the GEMMs: a window is cut into chunks of rows (a multiple of the minibatch
+// size).  Dispatch and combine kernels run on a second, internal stream with a bounded number of CTAs
+// (`num_comm_sms` x 8; they need no shared memory, so they share SMs with the resident GEMM CTAs), the GEMM /
+// SwiGLU kernels run on the caller's stream, and CUDA events at chunk granularity order them:
+//     comm:  dispatch(c) ------> record d[c]            wait y[c] -> combine(c)
+//     main:            wait d[c] -> GEMMs(c) -> record y[c]
+// Dispatch runs two chunks ahead.  The internal stream is forked from and joined back into the caller's stream
+// inside every call, so the caller sees ordinary stream semantics.  No kernel ever spins on another kernel.
+#include <stdlib.h>
+
 #include "comm.cuh"
 #include "elementwise.cuh"
 #include "grouped_gemm.cuh"
@@ -18,10 +29,69 @@ namespace {
         if (_rc != MOK_OK) return _rc; \
     } while (0)
 
+constexpr int kMaxEvents = 512;
+constexpr int kDefaultChunkRows = 32768;
+
+struct DeviceStreams {
+    cudaStream_t comm = nullptr;
+    cudaEvent_t events[kMaxEvents] = {};
+    int next = 0;
+    bool ready = false;
+};
+
+// One helper stream and an event pool per device, created on first use (single host thread per device).
+int streams_for_current_device(DeviceStreams** out) {
+    static DeviceStreams table[16];
+    int dev = 0;
+    MOK_CUDA_CHECK(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 16) return MOK_ERR_UNSUPPORTED;
+    DeviceStreams& d = table[dev];
+    if (!d.ready) {
+        int least = 0, greatest = 0;
+        MOK_CUDA_CHECK(cudaDeviceGetStreamPriorityRange(&least, &greatest));
+        MOK_CUDA_CHECK(cudaStreamCreateWithPriority(&d.comm, cudaStreamNonBlocking, greatest));
+        for (int i = 0; i < kMaxEvents; ++i) MOK_CUDA_CHECK(cudaEventCreateWithFlags(&d.events[i], cudaEventDisableTiming));
+        d.ready = true;
+    }
+    *out = &d;
+    return MOK_OK;
+}
+
+cudaEvent_t next_event(DeviceStreams* d) {
+    cudaEvent_t e = d->events[d->next];
+    d->next = (d->next + 1) % kMaxEvents;
+    return e;
+}
+
+// make `waiter` wait for everything enqueued on `signaller` so far
+int order_after(DeviceStreams* d, cudaStream_t signaller, cudaStream_t waiter) {
+    cudaEvent_t e = next_event(d);
+    MOK_CUDA_CHECK(cudaEventRecord(e, signaller));
+    MOK_CUDA_CHECK(cudaStreamWaitEvent(waiter, e, 0));
+    return MOK_OK;
+}
+
+bool overlap_enabled() {
+    const char* v = getenv("MOK_NO_OVERLAP");
+    return !(v != nullptr && v[0] == '1');
+}
+
+int chunk_rows_for(const mok_layer_args* a) {
+    int rows = kDefaultChunkRows;
+    if (const char* v = getenv("MOK_CHUNK_ROWS")) {
+        const int r = atoi(v);
+        if (r > 0) rows = r;
+    }
+    rows = (rows + a->minibatch_size - 1) / a->minibatch_size * a->minibatch_size;
+    // never more than ~100 chunks per window: events and launches stay bounded
+    const int min_rows = (a->macrobatch_size / 100 + a->minibatch_size) / a->minibatch_size * a->minibatch_size;
+    return rows < min_rows ? min_rows : rows;
+}
+
 int check_common(const mok_layer_args* a) {
     if (a == nullptr) return MOK_ERR_INVALID_ARGUMENT;
     if (a->ep_size < 1 || a->ep_size > MOK_MAX_EP || a->rank < 0 || a->rank >= a->ep_size) return MOK_ERR_INVALID_ARGUMENT;
-    if (a->num_local_tokens <= 0 || a->num_local_tokens % 128 != 0) return MOK_ERR_INVALID_ARGUMENT;
+    if (a->num_local_tokens <= 0 || a->num_local_tokens % 256 != 0) return MOK_ERR_INVALID_ARGUMENT;
     if (a->hidden <= 0 || a->hidden % 256 != 0 || a->intermediate <= 0 || a->intermediate % 256 != 0)
         return MOK_ERR_INVALID_ARGUMENT;
     if (a->num_local_experts < 1) return MOK_ERR_INVALID_ARGUMENT;
@@ -30,6 +100,7 @@ int check_common(const mok_layer_args* a) {
     if (a->schedule_capacity <= 0 || a->schedule_capacity % 256 != 0) return MOK_ERR_INVALID_ARGUMENT;
     if (a->minibatch_size <= 0 || a->minibatch_size % 256 != 0) return MOK_ERR_INVALID_ARGUMENT;
     if (a->macrobatch_size <= 0 || a->macrobatch_size % a->minibatch_size != 0) return MOK_ERR_INVALID_ARGUMENT;
+    if (a->num_comm_sms <= 0) return MOK_ERR_INVALID_ARGUMENT;
     if (!a->peer_rank || !a->peer_token_idx || !a->num_tokens || !a->tokens_per_expert) return MOK_ERR_INVALID_ARGUMENT;
     if (!a->x_ptrs || !a->x_local || !a->w_routed_gate || !a->w_routed_up) return MOK_ERR_INVALID_ARGUMENT;
     if (!a->x_routed || !a->gate_routed || !a->up_routed || !a->hidden_routed) return MOK_ERR_INVALID_ARGUMENT;
@@ -41,26 +112,48 @@ int check_common(const mok_layer_args* a) {
 
 int num_windows(const mok_layer_args* a) { return (a->schedule_capacity + a->macrobatch_size - 1) / a->macrobatch_size; }
 
-RowWindow window(const mok_layer_args* a, int w) {
+// rows [begin, end) of the schedule; `base` is the schedule row held by row 0 of the activation buffers
+struct Span {
+    int begin, end, base;
+};
+
+Span window_span(const mok_layer_args* a, int w) {
+    Span s;
+    s.begin = s.base = w * a->macrobatch_size;
+    s.end = s.begin + a->macrobatch_size;
+    if (s.end > a->schedule_capacity) s.end = a->schedule_capacity;
+    return s;
+}
+
+RowWindow rows_of(const mok_layer_args* a, const Span& s) {
     RowWindow r;
     r.peer_rank = a->peer_rank;
     r.peer_token = a->peer_token_idx;
     r.num_tokens = a->num_tokens;
-    r.row_begin = w * a->macrobatch_size;
-    r.row_end = r.row_begin + a->macrobatch_size;
-    if (r.row_end > a->schedule_capacity) r.row_end = a->schedule_capacity;
+    r.row_begin = s.begin;
+    r.row_end = s.end;
     r.status = a->status;
     return r;
 }
 
-GemmProblem routed_problem(const mok_layer_args* a, const RowWindow& w) {
+// activation buffer pointer of the span's first row
+template <typename T>
+T* at_row(T* buffer, const Span& s, int row_elems) {
+    return buffer + static_cast<size_t>(s.begin - s.base) * row_elems;
+}
+bf16* rows_bf16(void* buffer, const Span& s, int row_elems) { return at_row(static_cast<bf16*>(buffer), s, row_elems); }
+const bf16* rows_bf16(const void* buffer, const Span& s, int row_elems) {
+    return at_row(static_cast<const bf16*>(buffer), s, row_elems);
+}
+
+GemmProblem routed_problem(const mok_layer_args* a, const Span& s) {
     GemmProblem p;
     p.tokens_per_expert = a->tokens_per_expert;
     p.num_tokens = a->num_tokens;
     p.num_experts = a->num_local_experts;
-    p.row_begin = w.row_begin;
-    p.row_end = w.row_end;
-    p.buffer_rows = a->macrobatch_size;
+    p.row_begin = s.begin;
+    p.row_end = s.end;
+    p.buffer_rows = a->macrobatch_size - (s.begin - s.base);   // rows behind the (offset) buffer pointers
     p.status = a->status;
     return p;
 }
@@ -76,14 +169,20 @@ GemmProblem shared_problem(const mok_layer_args* a) {
     return p;
 }
 
-// dispatch x -> gate / up GEMMs -> SwiGLU for one window (used by forward, recompute and backward replay)
-int routed_up_to_hidden(const mok_layer_args* a, const RowWindow& w, cudaStream_t s) {
-    MOK_TRY(launch_dispatch(a->x_ptrs, nullptr, a->ep_size, w, a->topk, a->num_local_tokens, a->hidden, a->x_routed, nullptr, 0, s));
-    const GemmProblem p = routed_problem(a, w);
-    MOK_TRY(launch_rows_gemm(p, a->x_routed, a->hidden, a->w_routed_gate, a->w_routed_up, a->gate_routed, a->up_routed,
-                             a->intermediate, false, s));
-    MOK_TRY(launch_swiglu_fwd(a->gate_routed, a->up_routed, a->hidden_routed, a->num_tokens, 0, w.row_begin, w.row_end,
-                              a->intermediate, a->has_swiglu_limit != 0, a->swiglu_limit, s));
+int comm_ctas(const mok_layer_args* a, bool overlapped) { return overlapped ? a->num_comm_sms * 8 : 0; }
+
+// ---- per-span building blocks ---------------------------------------------------------------------------
+int dispatch_x(const mok_layer_args* a, const Span& s, int ctas, cudaStream_t st) {
+    return launch_dispatch(a->x_ptrs, nullptr, a->ep_size, rows_of(a, s), a->topk, a->num_local_tokens, a->hidden,
+                           rows_bf16(a->x_routed, s, a->hidden), nullptr, ctas, st);
+}
+
+int gate_up_hidden(const mok_layer_args* a, const Span& s, cudaStream_t st) {
+    const int H = a->hidden, I = a->intermediate;
+    MOK_TRY(launch_rows_gemm(routed_problem(a, s), rows_bf16(a->x_routed, s, H), H, a->w_routed_gate, a->w_routed_up,
+                             rows_bf16(a->gate_routed, s, I), rows_bf16(a->up_routed, s, I), I, false, st));
+    MOK_TRY(launch_swiglu_fwd(rows_bf16(a->gate_routed, s, I), rows_bf16(a->up_routed, s, I), rows_bf16(a->hidden_routed, s, I),
+                              a->num_tokens, 0, s.begin, s.end, I, a->has_swiglu_limit != 0, a->swiglu_limit, st));
     return MOK_OK;
 }
 
@@ -96,6 +195,56 @@ int shared_up_to_hidden(const mok_layer_args* a, cudaStream_t s) {
     return MOK_OK;
 }
 
+// ---- chunk pipeline -----------------------------------------------------------------------------------------
+// Runs pull(c) -> compute(c) -> push(c) over the chunks of one window.  Overlapped: pull / push on the internal
+// stream, compute on the caller's stream, ordered by events, pull two chunks ahead.  Not overlapped: one stream.
+// On return every pull has been consumed; pushes may still be running on the internal stream (the caller joins).
+template <class Pull, class Compute, class Push>
+int run_chunks(const mok_layer_args* a, const Span& win, bool overlapped, DeviceStreams* d, cudaStream_t main_stream,
+               Pull pull, Compute compute, Push push) {
+    const int chunk = chunk_rows_for(a);
+    const int n = (win.end - win.begin + chunk - 1) / chunk;
+    auto span_of = [&](int c) {
+        Span s;
+        s.base = win.base;
+        s.begin = win.begin + c * chunk;
+        s.end = s.begin + chunk < win.end ? s.begin + chunk : win.end;
+        return s;
+    };
+    if (!overlapped) {
+        for (int c = 0; c < n; ++c) {
+            const Span s = span_of(c);
+            MOK_TRY(pull(s, 0, main_stream));
+            MOK_TRY(compute(s, main_stream));
+            MOK_TRY(push(s, 0, main_stream));
+        }
+        return MOK_OK;
+    }
+    const int ctas = comm_ctas(a, true);
+    cudaEvent_t pulled[3], computed[3];   // rings: an event is re-recorded only after its waiter was enqueued
+    for (int i = 0; i < 3; ++i) {
+        pulled[i] = next_event(d);
+        computed[i] = next_event(d);
+    }
+    for (int step = 0; step < n + 2; ++step) {
+        const int c = step, m = step - 1, k = step - 2;
+        if (c < n) {
+            MOK_TRY(pull(span_of(c), ctas, d->comm));
+            MOK_CUDA_CHECK(cudaEventRecord(pulled[c % 3], d->comm));
+        }
+        if (m >= 0 && m < n) {
+            MOK_CUDA_CHECK(cudaStreamWaitEvent(main_stream, pulled[m % 3], 0));
+            MOK_TRY(compute(span_of(m), main_stream));
+            MOK_CUDA_CHECK(cudaEventRecord(computed[m % 3], main_stream));
+        }
+        if (k >= 0 && k < n) {
+            MOK_CUDA_CHECK(cudaStreamWaitEvent(d->comm, computed[k % 3], 0));
+            MOK_TRY(push(span_of(k), ctas, d->comm));
+        }
+    }
+    return MOK_OK;
+}
+
 }  // namespace
 }  // namespace mok
 
@@ -105,19 +254,37 @@ extern "C" int mok_moe_forward_bf16(const mok_layer_args* a, mok_stream_t stream
     if (!a->combine_ptrs || !a->w_routed_down || !a->y_routed) return MOK_ERR_INVALID_ARGUMENT;
     if (a->w_shared_gate && (!a->w_shared_down || !a->y_shared)) return MOK_ERR_INVALID_ARGUMENT;
     cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
-
-    if (a->w_shared_gate) {
+    const bool overlapped = overlap_enabled();
+    DeviceStreams* d = nullptr;
+    if (overlapped) {
+        MOK_TRY(streams_for_current_device(&d));
+        MOK_TRY(order_after(d, s, d->comm));   // fork: the internal stream starts after the caller's earlier work
+    }
+    const int H = a->hidden, I = a->intermediate;
+    if (a->w_shared_gate) {   // runs on the caller's stream while the first chunks are being pulled
         MOK_TRY(shared_up_to_hidden(a, s));
-        MOK_TRY(launch_rows_gemm(shared_problem(a), a->hidden_shared, a->intermediate, a->w_shared_down, nullptr, a->y_shared,
-                                 nullptr, a->hidden, false, s));
+        MOK_TRY(launch_rows_gemm(shared_problem(a), a->hidden_shared, I, a->w_shared_down, nullptr, a->y_shared, nullptr, H,
+                                 false, s));
     }
     for (int wi = num_windows(a) - 1; wi >= 0; --wi) {
-        const RowWindow w = window(a, wi);
-        MOK_TRY(routed_up_to_hidden(a, w, s));
-        MOK_TRY(launch_rows_gemm(routed_problem(a, w), a->hidden_routed, a->intermediate, a->w_routed_down, nullptr,
-                                 a->y_routed, nullptr, a->hidden, false, s));
-        MOK_TRY(launch_combine(a->combine_ptrs, nullptr, a->ep_size, w, a->topk, a->num_local_tokens, a->hidden, a->y_routed,
-                               nullptr, 0, s));
+        const Span win = window_span(a, wi);
+        MOK_TRY(run_chunks(
+            a, win, overlapped, d, s,
+            [&](const Span& c, int ctas, cudaStream_t st) { return dispatch_x(a, c, ctas, st); },
+            [&](const Span& c, cudaStream_t st) {
+                MOK_TRY(gate_up_hidden(a, c, st));
+                return launch_rows_gemm(routed_problem(a, c), rows_bf16(a->hidden_routed, c, I), I, a->w_routed_down, nullptr,
+                                        rows_bf16(a->y_routed, c, H), nullptr, H, false, st);
+            },
+            [&](const Span& c, int ctas, cudaStream_t st) {
+                return launch_combine(a->combine_ptrs, nullptr, a->ep_size, rows_of(a, c), a->topk, a->num_local_tokens, H,
+                                      rows_bf16(a->y_routed, c, H), nullptr, ctas, st);
+            }));
+        // the next window reuses the buffers: its pulls wait for this window's GEMMs, its GEMMs for these pushes
+        if (overlapped) {
+            MOK_TRY(order_after(d, d->comm, s));
+            if (wi > 0) MOK_TRY(order_after(d, s, d->comm));
+        }
     }
     return MOK_OK;
 }
@@ -127,7 +294,9 @@ extern "C" int mok_moe_recompute_bf16(const mok_layer_args* a, mok_stream_t stre
     MOK_TRY(check_common(a));
     cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
     if (a->w_shared_gate) MOK_TRY(shared_up_to_hidden(a, s));
-    MOK_TRY(routed_up_to_hidden(a, window(a, 0), s));
+    const Span win = window_span(a, 0);
+    MOK_TRY(dispatch_x(a, win, 0, s));
+    MOK_TRY(gate_up_hidden(a, win, s));
     return MOK_OK;
 }
 
@@ -146,6 +315,12 @@ extern "C" int mok_moe_backward_bf16(const mok_layer_args* a, mok_stream_t strea
     cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
     const int H = a->hidden, I = a->intermediate, T = a->num_local_tokens;
     const bool clamp = a->has_swiglu_limit != 0;
+    const bool overlapped = overlap_enabled();
+    DeviceStreams* d = nullptr;
+    if (overlapped) {
+        MOK_TRY(streams_for_current_device(&d));
+        MOK_TRY(order_after(d, s, d->comm));
+    }
 
     if (shared) {
         const GemmProblem p = shared_problem(a);
@@ -165,19 +340,41 @@ extern "C" int mok_moe_backward_bf16(const mok_layer_args* a, mok_stream_t strea
     float* row_weight = a->row_scratch;
     float* row_grad = a->row_scratch + a->macrobatch_size;
     for (int wi = 0; wi < num_windows(a); ++wi) {
-        const RowWindow w = window(a, wi);
-        const GemmProblem p = routed_problem(a, w);
-        if (wi > 0) MOK_TRY(routed_up_to_hidden(a, w, s));   // the saved context only covers window 0
-        MOK_TRY(launch_dispatch(a->d_y_ptrs, a->router_weight_ptrs, a->ep_size, w, a->topk, T, H, a->d_y_routed, row_weight, 0, s));
-        MOK_TRY(launch_rows_gemm(p, a->d_y_routed, H, a->w_routed_down, nullptr, a->d_hidden_routed, nullptr, I, true, s));
-        MOK_TRY(launch_swiglu_bwd(a->gate_routed, a->up_routed, a->d_hidden_routed, a->d_gate_routed, a->d_up_routed,
-                                  a->num_tokens, 0, w.row_begin, w.row_end, I, clamp, a->swiglu_limit, row_weight, row_grad, s));
-        MOK_TRY(launch_rows_gemm_dual(p, a->d_gate_routed, a->d_up_routed, I, a->w_routed_gate, a->w_routed_up, a->d_x_routed, H, s));
+        const Span win = window_span(a, wi);
+        if (wi > 0) {   // the saved context only covers window 0: rebuild x_routed, gate, up, hidden of this window
+            MOK_TRY(dispatch_x(a, win, 0, s));
+            MOK_TRY(gate_up_hidden(a, win, s));
+        }
+        MOK_TRY(run_chunks(
+            a, win, overlapped, d, s,
+            [&](const Span& c, int ctas, cudaStream_t st) {
+                return launch_dispatch(a->d_y_ptrs, a->router_weight_ptrs, a->ep_size, rows_of(a, c), a->topk, T, H,
+                                       rows_bf16(a->d_y_routed, c, H), at_row(row_weight, c, 1), ctas, st);
+            },
+            [&](const Span& c, cudaStream_t st) {
+                const GemmProblem p = routed_problem(a, c);
+                MOK_TRY(launch_rows_gemm(p, rows_bf16(a->d_y_routed, c, H), H, a->w_routed_down, nullptr,
+                                         rows_bf16(a->d_hidden_routed, c, I), nullptr, I, true, st));
+                MOK_TRY(launch_swiglu_bwd(rows_bf16(a->gate_routed, c, I), rows_bf16(a->up_routed, c, I),
+                                          rows_bf16(a->d_hidden_routed, c, I), rows_bf16(a->d_gate_routed, c, I),
+                                          rows_bf16(a->d_up_routed, c, I), a->num_tokens, 0, c.begin, c.end, I, clamp,
+                                          a->swiglu_limit, at_row(row_weight, c, 1), at_row(row_grad, c, 1), st));
+                return launch_rows_gemm_dual(p, rows_bf16(a->d_gate_routed, c, I), rows_bf16(a->d_up_routed, c, I), I,
+                                             a->w_routed_gate, a->w_routed_up, rows_bf16(a->d_x_routed, c, H), H, st);
+            },
+            [&](const Span& c, int ctas, cudaStream_t st) {
+                return launch_combine(a->d_x_routed_ptrs, a->d_router_weight_ptrs, a->ep_size, rows_of(a, c), a->topk, T, H,
+                                      rows_bf16(a->d_x_routed, c, H), at_row(row_grad, c, 1), ctas, st);
+            }));
+        // weight gradients over the whole window (fixed K order = schedule order), while the last pushes drain
+        const GemmProblem p = routed_problem(a, win);
         MOK_TRY(launch_wgrad_gemm(p, a->d_y_routed, H, a->hidden_routed, I, a->d_w_routed_down, s));
         MOK_TRY(launch_wgrad_gemm(p, a->d_gate_routed, I, a->x_routed, H, a->d_w_routed_gate, s));
         MOK_TRY(launch_wgrad_gemm(p, a->d_up_routed, I, a->x_routed, H, a->d_w_routed_up, s));
-        MOK_TRY(launch_combine(a->d_x_routed_ptrs, a->d_router_weight_ptrs, a->ep_size, w, a->topk, T, H, a->d_x_routed,
-                               row_grad, 0, s));
+        if (overlapped) {
+            MOK_TRY(order_after(d, d->comm, s));
+            if (wi + 1 < num_windows(a)) MOK_TRY(order_after(d, s, d->comm));
+        }
     }
     MOK_TRY(launch_zero_empty_wgrads(a->tokens_per_expert, a->num_local_experts, a->d_w_routed_gate, a->d_w_routed_up,
                                      a->d_w_routed_down, static_cast<long long>(H) * I, s));

@@ -89,6 +89,25 @@ def test_layer_with_recomputed_context_and_bitwise_repeat(dist_ctx):
         assert torch.equal(a, b), f"{name} is not bitwise reproducible"
 
 
+def test_chunked_two_stream_pipeline_equals_single_stream(dist_ctx, monkeypatch):
+    """Dispatch / combine on the internal stream with many small chunks gives bit-identical results to the plain
+    single-stream order (same kernels, same per-element arithmetic)."""
+    import mok
+    E, H, I, K, T = 8, 256, 256, 4, 1024
+    config = mok.functional.MoKConfig(minibatch_size=256, macrobatch_size=2048)
+    inp = O.make_rank_inputs(0, E, E, K, T, H, I)
+    monkeypatch.setenv("MOK_NO_OVERLAP", "1")
+    out_a, grads_a = _run(dist_ctx, inp, E, config)
+    monkeypatch.delenv("MOK_NO_OVERLAP")
+    monkeypatch.setenv("MOK_CHUNK_ROWS", "256")
+    out_b, grads_b = _run(dist_ctx, inp, E, config)
+    monkeypatch.delenv("MOK_CHUNK_ROWS")
+    _compare(O.moe_layer_oracle([inp])[0], out_b, grads_b, "chunked")
+    assert torch.equal(out_a, out_b)
+    for name, a, b in zip(FIELDS, grads_a, grads_b):
+        assert torch.equal(a, b), name
+
+
 def test_degenerate_routing_all_tokens_pick_first_experts(dist_ctx):
     import mok
     E, H, I, K, T = 16, 256, 256, 8, 512
