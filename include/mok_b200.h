@@ -219,6 +219,25 @@ int mok_grouped_wgrad_bf16(const void* A, const void* B, void* D, const int32_t*
                            const int32_t* num_tokens, int num_experts, int rows, int M, int N,
                            uint32_t* status, mok_stream_t stream);
 
+/*
+ * MXFP8 grouped GEMM, one launch: D[rows, N] (bf16) = A[rows, K] * B[e]^T with A, B in e4m3 and e8m0 scales per 32
+ * elements along K in the [rows/128, K/128, 32, 16] layout that mok_mxfp8_quantize writes; B is [E, N, K] with
+ * scales [E*N/128, K/128, 32, 16].  Replaces the MXFP8 form of expert_grouped_gemm_kernel
+ * (csrc/megakernel/grouped_gemm.cuh:222-249, block-scaled mm2_ABt).  rows, N multiples of 256; K of 128.
+ */
+int mok_grouped_gemm_mxfp8(const void* A_fp8, const void* A_sc, const void* B_fp8, const void* B_sc, void* D,
+                           const int32_t* tokens_per_expert, const int32_t* num_tokens, int num_experts, int rows,
+                           int N, int K, uint32_t* status, mok_stream_t stream);
+
+/*
+ * MXFP8 weight-gradient form: D[e] [M, N] (bf16) = At[:, rows_e] * Bt[:, rows_e]^T where At [M, rows] and Bt [N, rows]
+ * are transposed-quantized activations (scales along the row dimension of the schedule).  Replaces the MXFP8 wgrad
+ * use of the reference grouped GEMM (csrc/megakernel/backward.cuh:369-403).
+ */
+int mok_grouped_wgrad_mxfp8(const void* At_fp8, const void* At_sc, const void* Bt_fp8, const void* Bt_sc, void* D,
+                            const int32_t* tokens_per_expert, const int32_t* num_tokens, int num_experts, int rows,
+                            int M, int N, uint32_t* status, mok_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -207,6 +207,37 @@ __device__ __forceinline__ void umma_commit_pair(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
                  ::"r"(bar), "h"(both) : "memory");
 }
+// ---- block-scaled MXFP8 (e4m3 data, e8m0 scale per 32 elements along K) -------------------------------------
+// Shared-memory descriptor of one 512-byte scale tile (32 rows x 16 bytes, no swizzle): 8-row groups 128 B apart.
+__device__ __forceinline__ uint64_t umma_scale_desc(uint32_t saddr) {
+    uint64_t d = 0;
+    d |= static_cast<uint64_t>((saddr & 0x3FFFFu) >> 4);
+    d |= static_cast<uint64_t>(128u >> 4) << 32;
+    d |= 1ull << 46;
+    return d;
+}
+// Copies a scale tile from each CTA's shared memory into the same tensor-memory columns of each CTA; the 32
+// source rows are replicated to all four lane quarters.
+__device__ __forceinline__ void tmem_copy_scales_pair(uint32_t taddr, uint64_t sdesc) {
+    asm volatile("tcgen05.cp.cta_group::2.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(sdesc) : "memory");
+}
+// Instruction descriptor for kind::mxf8f6f4.block_scale, e4m3 x e4m3 -> fp32, both operands K-major, e8m0 scales.
+// Bits: B scale id at 4, A/B formats (0 = e4m3) at 7 / 10, N >> 3 at 17, scale format (1 = e8m0) at 23, M >> 4 at
+// 24, A scale id at 29.  The scale id picks which byte of the 32-bit scale column belongs to this K slice of 32.
+__host__ __device__ constexpr uint32_t umma_idesc_mxfp8(int m, int n, uint32_t sf_id) {
+    return (sf_id << 4) | (static_cast<uint32_t>(n >> 3) << 17) | (1u << 23) | (static_cast<uint32_t>(m >> 4) << 24) |
+           (sf_id << 29);
+}
+__device__ __forceinline__ void umma_mxfp8_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                                uint32_t sfa_tmem, uint32_t sfb_tmem, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::mxf8f6f4.block_scale [%0], %1, %2, %3, [%5], [%6], p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(sfa_tmem), "r"(sfb_tmem)
+        : "memory");
+}
+
 // Arrive on an mbarrier of the leader CTA from either CTA of the pair.
 __device__ __forceinline__ void mbar_arrive_leader(uint32_t bar) {
     asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(bar & kPairLeaderMask) : "memory");

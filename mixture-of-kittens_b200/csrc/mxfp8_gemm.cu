@@ -1,0 +1,572 @@
+// Block-scaled MXFP8 grouped GEMM for sm_100a: tcgen05.mma kind::mxf8f6f4.block_scale on CTA pairs.
+//
+// Same structure as the bf16 kernel (grouped_gemm.cu): a cluster of two CTAs owns a 256 x 256 output tile, each
+// CTA stages its 128 rows of A and its 128-column half of B by TMA (K step 128 bytes = 128 e4m3 elements), the
+// leader CTA issues the MMAs.  In addition every K step carries its e8m0 scales: one 512-byte tile for the CTA's
+// 128 rows of A and two for the 256 columns of B (both CTAs need all B scales), loaded by TMA next to the data,
+// copied to tensor memory with tcgen05.cp and consumed by four K = 32 MMAs whose descriptor selects the scale byte.
+// Tensor memory: 256 accumulator columns + 12 scale columns, so the accumulator is single-buffered.
+// Both operands are K-major; the dgrad and wgrad forms use transposed-quantized copies of weights / activations
+// (the role MXFP8 plays in the reference grouped GEMM, csrc/megakernel/grouped_gemm.cuh:222-249).
+#include "mxfp8_gemm.cuh"
+
+namespace mok {
+namespace {
+
+constexpr int BM = 256, BM_CTA = 128, BN = 256, BN_CTA = 128;
+constexpr int BK = 128;                               // e4m3 elements = bytes per K step
+constexpr int STAGES = 6;
+constexpr int A_TILE_BYTES = BM_CTA * BK;             // 16 KB
+constexpr int B_TILE_BYTES = BN_CTA * BK;             // 16 KB
+constexpr int DATA_STAGE_BYTES = A_TILE_BYTES + B_TILE_BYTES;
+constexpr int SCALE_TILE_BYTES = 512;
+constexpr int SCALE_STAGE_BYTES = 3 * SCALE_TILE_BYTES;   // A rows of this CTA, B columns [0,128), B columns [128,256)
+constexpr int STAGE_TX_BYTES = DATA_STAGE_BYTES + SCALE_STAGE_BYTES;
+constexpr int NUM_THREADS = 192;
+constexpr int TMEM_COLS = 512;
+constexpr int TMEM_SFA_COL = 256;                     // 4 columns
+constexpr int TMEM_SFB_COL = 260;                     // 8 columns
+constexpr int MODE_ROWS = 0;
+constexpr int MODE_WGRAD = 1;
+
+struct KernelParams {
+    const int32_t* tokens_per_expert;
+    const int32_t* num_tokens;
+    int num_experts;
+    int dense_rows;
+    int row_begin, row_end;
+    int n_blocks;     // N / 256 (per output set in rows mode)
+    int m_blocks_w;   // wgrad: M / 256
+    int k_blocks;     // rows: K / 128 per operand set
+    int n_sets, k_sets;
+    int n_tiles_per_expert;   // rows: N / 128, scale row tiles of one expert's weight
+    bf16* D0;
+    bf16* D1;
+    long long ldd;
+    long long d_expert_stride;
+    uint32_t* status;
+};
+
+struct Tile {
+    int expert, row0, m0, n0, set, k_blocks, accumulate;
+};
+
+struct SharedLayout {
+    static constexpr int kScales = STAGES * DATA_STAGE_BYTES;
+    static constexpr int kFull = kScales + STAGES * SCALE_STAGE_BYTES;
+    static constexpr int kEmpty = kFull + 8 * STAGES;
+    static constexpr int kTmemFull = kEmpty + 8 * STAGES;
+    static constexpr int kTmemEmpty = kTmemFull + 8;
+    static constexpr int kTmemPtr = kTmemEmpty + 8;
+    static constexpr int kAbort = kTmemPtr + 4;
+    static constexpr int kCum = kAbort + 4 + 8;
+};
+
+template <int MODE>
+__device__ __forceinline__ bool decode_tile(const KernelParams& p, const int* cum, int lo, int hi, int t, Tile& tile) {
+    if (MODE == MODE_ROWS) {
+        const int per_m = p.n_blocks * p.n_sets;
+        const int mt = t / per_m;
+        const int rem = t - mt * per_m;
+        tile.set = rem / p.n_blocks;
+        tile.n0 = (rem - tile.set * p.n_blocks) * BN;
+        tile.row0 = lo + mt * BM;
+        tile.m0 = 0;
+        int e = 0;
+        if (p.tokens_per_expert != nullptr) {
+            int a = 0, b = p.num_experts;
+            while (b - a > 1) {
+                const int mid = (a + b) >> 1;
+                if (cum[mid] <= tile.row0) a = mid; else b = mid;
+            }
+            e = a;
+        }
+        tile.expert = e;
+        tile.k_blocks = p.k_blocks * p.k_sets;
+        tile.accumulate = 0;
+        return true;
+    } else {
+        const int per_e = p.m_blocks_w * p.n_blocks;
+        const int e = t / per_e;
+        const int rem = t - e * per_e;
+        const int mi = rem / p.n_blocks;
+        tile.expert = e;
+        tile.m0 = mi * BM;
+        tile.n0 = (rem - mi * p.n_blocks) * BN;
+        tile.set = 0;
+        const int ks = max(cum[e], lo);
+        const int ke = min(cum[e + 1], hi);
+        tile.row0 = ks;
+        tile.k_blocks = ke > ks ? (ke - ks) / BK : 0;
+        tile.accumulate = cum[e] < lo ? 1 : 0;
+        return tile.k_blocks > 0;
+    }
+}
+
+__device__ __forceinline__ void store_row_chunk(bf16* dst, const uint32_t (&acc)[32], bool accumulate) {
+    uint4* out = reinterpret_cast<uint4*>(dst);
+#pragma unroll
+    for (int v = 0; v < 4; ++v) {
+        float f[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) f[i] = __uint_as_float(acc[v * 8 + i]);
+        if (accumulate) {
+            const uint4 old = out[v];
+            const float2 o0 = unpack_bf16x2(old.x), o1 = unpack_bf16x2(old.y), o2 = unpack_bf16x2(old.z), o3 = unpack_bf16x2(old.w);
+            f[0] += o0.x; f[1] += o0.y; f[2] += o1.x; f[3] += o1.y;
+            f[4] += o2.x; f[5] += o2.y; f[6] += o3.x; f[7] += o3.y;
+        }
+        uint4 w;
+        w.x = pack_bf16x2(f[0], f[1]);
+        w.y = pack_bf16x2(f[2], f[3]);
+        w.z = pack_bf16x2(f[4], f[5]);
+        w.w = pack_bf16x2(f[6], f[7]);
+        out[v] = w;
+    }
+}
+
+// One operand set: data and scale tensor maps of A and B.
+struct MapSet {
+    CUtensorMap a, sfa, b, sfb;
+};
+
+template <int MODE>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+mxfp8_gemm_kernel(const __grid_constant__ MapSet ms0, const __grid_constant__ MapSet ms1, const KernelParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+    const uint32_t scale_base = smem_base + SharedLayout::kScales;
+    const uint32_t bar_full = smem_base + SharedLayout::kFull;
+    const uint32_t bar_empty = smem_base + SharedLayout::kEmpty;
+    const uint32_t bar_tmem_full = smem_base + SharedLayout::kTmemFull;
+    const uint32_t bar_tmem_empty = smem_base + SharedLayout::kTmemEmpty;
+    volatile uint32_t* tmem_ptr_slot = reinterpret_cast<volatile uint32_t*>(smem_gen + SharedLayout::kTmemPtr);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_gen + SharedLayout::kAbort);
+    int* cum = reinterpret_cast<int*>(smem_gen + SharedLayout::kCum);
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const int cta_rank = static_cast<int>(cluster_cta_rank());
+    const int pair = blockIdx.x >> 1;
+    const int num_pairs = gridDim.x >> 1;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(bar_full + 8 * s, 1);
+            mbar_init(bar_empty + 8 * s, 1);
+        }
+        mbar_init(bar_tmem_full, 1);
+        mbar_init(bar_tmem_empty, 8);
+        *abort_flag = 0;
+        mbar_fence_init();
+        tma_prefetch_desc(&ms0.a); tma_prefetch_desc(&ms0.sfa); tma_prefetch_desc(&ms0.b); tma_prefetch_desc(&ms0.sfb);
+        if (p.k_sets > 1 || p.n_sets > 1) { tma_prefetch_desc(&ms1.b); tma_prefetch_desc(&ms1.sfb); }
+        if (p.k_sets > 1) { tma_prefetch_desc(&ms1.a); tma_prefetch_desc(&ms1.sfa); }
+    }
+    if (warp == 1) {
+        tmem_alloc_pair(smem_u32(const_cast<uint32_t*>(tmem_ptr_slot)), TMEM_COLS);
+        tmem_relinquish_pair();
+    }
+    if (warp == 2) {
+        if (p.tokens_per_expert == nullptr) {
+            if (lane == 0) { cum[0] = 0; cum[1] = p.dense_rows; }
+        } else {
+            int carry = 0;
+            if (lane == 0) cum[0] = 0;
+            for (int base = 0; base < p.num_experts; base += 32) {
+                const int idx = base + lane;
+                int v = idx < p.num_experts ? p.tokens_per_expert[idx] : 0;
+#pragma unroll
+                for (int off = 1; off < 32; off <<= 1) {
+                    const int n = __shfl_up_sync(0xffffffffu, v, off);
+                    if (lane >= off) v += n;
+                }
+                if (idx < p.num_experts) cum[idx + 1] = carry + v;
+                carry += __shfl_sync(0xffffffffu, v, 31);
+            }
+        }
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    cluster_sync_all();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = *tmem_ptr_slot;
+
+    const int total_rows = p.tokens_per_expert == nullptr ? p.dense_rows : *p.num_tokens;
+    const int lo = p.row_begin;
+    const int hi = min(p.row_end, total_rows);
+    int total_tiles;
+    if (MODE == MODE_ROWS) total_tiles = hi > lo ? ((hi - lo) / BM) * p.n_blocks * p.n_sets : 0;
+    else total_tiles = hi > lo ? p.num_experts * p.m_blocks_w * p.n_blocks : 0;
+
+    if (warp == 0) {
+        // ---- TMA producer (both CTAs): data tiles and scale tiles of one K step land on the leader's barrier ----
+        int stage = 0;
+        uint32_t phase = 0;
+        bool ok = true;
+        for (int t = pair; t < total_tiles && ok; t += num_pairs) {
+            Tile tile;
+            if (!decode_tile<MODE>(p, cum, lo, hi, t, tile)) continue;
+            for (int kb = 0; kb < tile.k_blocks; ++kb) {
+                ok = mbar_wait(bar_empty + 8 * stage, phase ^ 1u, abort_flag, p.status);
+                if (!ok) break;
+                if (lane == 0) {
+                    const uint32_t full_local = bar_full + 8 * stage;
+                    const uint32_t full = full_local & kPairLeaderMask;
+                    const uint32_t a_dst = smem_base + stage * DATA_STAGE_BYTES;
+                    const uint32_t b_dst = a_dst + A_TILE_BYTES;
+                    const uint32_t s_dst = scale_base + stage * SCALE_STAGE_BYTES;
+                    if (cta_rank == 0) mbar_expect_tx(full_local, 2 * STAGE_TX_BYTES);
+                    if (MODE == MODE_ROWS) {
+                        const int kset = kb >= p.k_blocks ? 1 : 0;
+                        const int kt = kb - kset * p.k_blocks;           // K tile of 128
+                        const MapSet& am = kset ? ms1 : ms0;
+                        const MapSet& bm = (kset || tile.set) ? ms1 : ms0;
+                        const int row = tile.row0 - p.row_begin + cta_rank * BM_CTA;
+                        tma_load_4d_pair(a_dst, &am.a, full, kt * BK, row, 0, 0);
+                        tma_load_4d_pair(s_dst, &am.sfa, full, 0, kt, row / 128, 0);
+                        tma_load_4d_pair(b_dst, &bm.b, full, kt * BK, tile.n0 + cta_rank * BN_CTA, tile.expert, 0);
+                        const int sfb_row = tile.expert * p.n_tiles_per_expert + tile.n0 / 128;
+                        tma_load_4d_pair(s_dst + SCALE_TILE_BYTES, &bm.sfb, full, 0, kt, sfb_row, 0);
+                        tma_load_4d_pair(s_dst + 2 * SCALE_TILE_BYTES, &bm.sfb, full, 0, kt, sfb_row + 1, 0);
+                    } else {
+                        const int kcol = tile.row0 + kb * BK - p.row_begin;   // column of the transposed activations
+                        tma_load_4d_pair(a_dst, &ms0.a, full, kcol, tile.m0 + cta_rank * BM_CTA, 0, 0);
+                        tma_load_4d_pair(s_dst, &ms0.sfa, full, 0, kcol / 128, tile.m0 / 128 + cta_rank, 0);
+                        tma_load_4d_pair(b_dst, &ms0.b, full, kcol, tile.n0 + cta_rank * BN_CTA, 0, 0);
+                        tma_load_4d_pair(s_dst + SCALE_TILE_BYTES, &ms0.sfb, full, 0, kcol / 128, tile.n0 / 128, 0);
+                        tma_load_4d_pair(s_dst + 2 * SCALE_TILE_BYTES, &ms0.sfb, full, 0, kcol / 128, tile.n0 / 128 + 1, 0);
+                    }
+                }
+                __syncwarp();
+                if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+            }
+        }
+    } else if (warp == 1) {
+        // ---- MMA issuer (leader CTA only) ----------------------------------------------------------------
+        if (cta_rank == 0) {
+            int stage = 0;
+            uint32_t phase = 0;
+            int iter = 0;
+            bool ok = true;
+            const uint32_t sfa_tmem = tmem_base + TMEM_SFA_COL;
+            const uint32_t sfb_tmem = tmem_base + TMEM_SFB_COL;
+            for (int t = pair; t < total_tiles && ok; t += num_pairs) {
+                Tile tile;
+                if (!decode_tile<MODE>(p, cum, lo, hi, t, tile)) continue;
+                ok = mbar_wait(bar_tmem_empty, (iter & 1u) ^ 1u, abort_flag, p.status);   // epilogue drained the accumulator
+                if (!ok) break;
+                tc_fence_after_sync();
+                for (int kb = 0; kb < tile.k_blocks; ++kb) {
+                    ok = mbar_wait(bar_full + 8 * stage, phase, abort_flag, p.status);
+                    if (!ok) break;
+                    tc_fence_after_sync();
+                    if (lane == 0) {
+                        const uint32_t a_addr = smem_base + stage * DATA_STAGE_BYTES;
+                        const uint32_t b_addr = a_addr + A_TILE_BYTES;
+                        const uint32_t s_addr = scale_base + stage * SCALE_STAGE_BYTES;
+                        tmem_copy_scales_pair(sfa_tmem, umma_scale_desc(s_addr));
+                        tmem_copy_scales_pair(sfb_tmem, umma_scale_desc(s_addr + SCALE_TILE_BYTES));
+                        tmem_copy_scales_pair(sfb_tmem + 4, umma_scale_desc(s_addr + 2 * SCALE_TILE_BYTES));
+                        const uint64_t a_desc = umma_smem_desc(a_addr, 16, 1024);
+                        const uint64_t b_desc = umma_smem_desc(b_addr, 16, 1024);
+#pragma unroll
+                        for (int k = 0; k < BK / 32; ++k)   // 32 elements = 32 bytes = 2 descriptor units per slice
+                            umma_mxfp8_pair(tmem_base, a_desc + k * 2u, b_desc + k * 2u, umma_idesc_mxfp8(BM, BN, k), sfa_tmem,
+                                            sfb_tmem, (kb | k) != 0 ? 1u : 0u);
+                        umma_commit_pair(bar_empty + 8 * stage);
+                        if (kb == tile.k_blocks - 1) umma_commit_pair(bar_tmem_full);
+                    }
+                    __syncwarp();
+                    if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+                }
+                ++iter;
+            }
+        }
+    } else {
+        // ---- epilogue --------------------------------------------------------------------------------------
+        const int quarter = warp & 3;
+        const int row_in_tile = cta_rank * BM_CTA + quarter * 32 + lane;
+        int iter = 0;
+        bool ok = true;
+        for (int t = pair; t < total_tiles && ok; t += num_pairs) {
+            Tile tile;
+            if (!decode_tile<MODE>(p, cum, lo, hi, t, tile)) continue;
+            ok = mbar_wait(bar_tmem_full, iter & 1u, abort_flag, p.status);
+            if (!ok) break;
+            tc_fence_after_sync();
+            bf16* out;
+            if (MODE == MODE_ROWS)
+                out = (tile.set ? p.D1 : p.D0) + static_cast<long long>(tile.row0 - p.row_begin + row_in_tile) * p.ldd + tile.n0;
+            else
+                out = p.D0 + static_cast<long long>(tile.expert) * p.d_expert_stride +
+                      static_cast<long long>(tile.m0 + row_in_tile) * p.ldd + tile.n0;
+            const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
+#pragma unroll 1
+            for (int c = 0; c < BN / 32; ++c) {
+                uint32_t v[32];
+                tmem_ld_32x32(taddr + c * 32, v);
+                tmem_ld_wait();
+                store_row_chunk(out + c * 32, v, tile.accumulate != 0);
+            }
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_leader(bar_tmem_empty);
+            ++iter;
+        }
+    }
+
+    if (*abort_flag) {
+        for (int i = 0; i < 64; ++i) __nanosleep(2000);
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    cluster_sync_all();
+    if (warp == 1) {
+        tc_fence_after_sync();
+        tmem_dealloc_pair(tmem_base, TMEM_COLS);
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// Host side
+// ---------------------------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (fn == nullptr) {
+        void* sym = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres) == cudaSuccess &&
+            qres == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(sym);
+    }
+    return fn;
+}
+
+int encode(CUtensorMap* map, CUtensorMapDataType type, const void* base, const cuuint64_t (&dims)[4],
+           const cuuint64_t (&strides)[3], const cuuint32_t (&box)[4], CUtensorMapSwizzle swizzle) {
+    EncodeTiledFn fn = encode_fn();
+    if (fn == nullptr) {
+        set_last_error("cuTensorMapEncodeTiled unavailable", cudaErrorNotSupported);
+        return MOK_ERR_CUDA;
+    }
+    cuuint32_t estr[4] = {1, 1, 1, 1};
+    CUresult r = fn(map, type, 4, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle,
+                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        set_last_error("cuTensorMapEncodeTiled failed (mxfp8)", cudaErrorInvalidValue);
+        return MOK_ERR_CUDA;
+    }
+    return MOK_OK;
+}
+
+// e4m3 bytes [groups][rows_per_group][k]: box 128 (K) x 128 (rows)
+int data_map(CUtensorMap* map, const Fp8Operand& op, long long rows_per_group, long long groups) {
+    const cuuint64_t dims[4] = {static_cast<cuuint64_t>(op.k_extent), static_cast<cuuint64_t>(rows_per_group),
+                                static_cast<cuuint64_t>(groups), 1};
+    const cuuint64_t strides[3] = {static_cast<cuuint64_t>(op.ld), static_cast<cuuint64_t>(op.ld * rows_per_group),
+                                   static_cast<cuuint64_t>(op.ld * rows_per_group * groups)};
+    const cuuint32_t box[4] = {BK, 128, 1, 1};
+    return encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, op.data, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
+}
+
+// scale tiles [row tile][K tile][128 words]: one 512-byte tile per copy
+int scale_map(CUtensorMap* map, const Fp8Operand& op) {
+    const long long k_tiles = op.k_extent / 128;
+    const long long row_tiles = op.rows / 128;
+    const cuuint64_t dims[4] = {128, static_cast<cuuint64_t>(k_tiles), static_cast<cuuint64_t>(row_tiles), 1};
+    const cuuint64_t strides[3] = {512, static_cast<cuuint64_t>(op.scale_row_tile_stride),
+                                   static_cast<cuuint64_t>(op.scale_row_tile_stride * row_tiles)};
+    const cuuint32_t box[4] = {128, 1, 1, 1};
+    return encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT32, op.scales, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_NONE);
+}
+
+bool operand_ok(const Fp8Operand& op) {
+    return op.data != nullptr && op.scales != nullptr && op.ld > 0 && op.ld % 128 == 0 && op.rows > 0 && op.rows % 128 == 0 &&
+           op.k_extent > 0 && op.k_extent % 128 == 0 && op.scale_row_tile_stride >= 512 && op.scale_row_tile_stride % 512 == 0 &&
+           (reinterpret_cast<uintptr_t>(op.data) & 127) == 0 && (reinterpret_cast<uintptr_t>(op.scales) & 127) == 0;
+}
+
+int fill_set(MapSet* ms, const Fp8Operand& a, long long a_groups, const Fp8Operand& b, long long b_groups) {
+    if (!operand_ok(a) || !operand_ok(b)) return MOK_ERR_INVALID_ARGUMENT;
+    int rc;
+    if ((rc = data_map(&ms->a, a, a.rows / a_groups, a_groups)) != MOK_OK) return rc;
+    if ((rc = scale_map(&ms->sfa, a)) != MOK_OK) return rc;
+    if ((rc = data_map(&ms->b, b, b.rows / b_groups, b_groups)) != MOK_OK) return rc;
+    return scale_map(&ms->sfb, b);
+}
+
+size_t smem_bytes(int num_experts) { return 1024 + SharedLayout::kCum + 4 * (static_cast<size_t>(num_experts) + 2); }
+constexpr int kMaxDynamicSmem = 232448 - 1024;
+
+template <int MODE>
+int launch(const MapSet& ms0, const MapSet& ms1, const KernelParams& kp, int max_tiles, cudaStream_t stream) {
+    auto kernel = mxfp8_gemm_kernel<MODE>;
+    static int max_pairs[16] = {0};
+    int dev = 0;
+    MOK_CUDA_CHECK(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 16) return MOK_ERR_UNSUPPORTED;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cudaLaunchConfig_t cfg = {};
+    cfg.blockDim = dim3(NUM_THREADS);
+    cfg.dynamicSmemBytes = smem_bytes(kp.num_experts);
+    cfg.stream = stream;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    if (max_pairs[dev] == 0) {
+        MOK_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxDynamicSmem));
+        cfg.gridDim = dim3(2 * sm_count());
+        const size_t keep = cfg.dynamicSmemBytes;
+        cfg.dynamicSmemBytes = kMaxDynamicSmem;
+        int clusters = 0;
+        MOK_CUDA_CHECK(cudaOccupancyMaxActiveClusters(&clusters, kernel, &cfg));
+        cfg.dynamicSmemBytes = keep;
+        max_pairs[dev] = clusters > 0 ? clusters : sm_count() / 2;
+    }
+    int pairs = max_pairs[dev] < max_tiles ? max_pairs[dev] : max_tiles;
+    if (pairs <= 0) return MOK_OK;
+    cfg.gridDim = dim3(2 * pairs);
+    cudaError_t err = cudaLaunchKernelEx(&cfg, kernel, ms0, ms1, kp);
+    if (err != cudaSuccess) return fail_cuda("mxfp8_gemm_kernel launch", err);
+    MOK_LAUNCH_CHECK("mxfp8_gemm_kernel");
+    return MOK_OK;
+}
+
+int check_problem(const GemmProblem& pb) {
+    if (pb.num_experts < 1 || pb.num_experts > MOK_MAX_LOCAL_EXPERTS) return MOK_ERR_TOO_LARGE;
+    if (pb.row_begin < 0 || pb.row_end < pb.row_begin || (pb.row_begin % BM) != 0 || (pb.row_end % BM) != 0)
+        return MOK_ERR_INVALID_ARGUMENT;
+    if (pb.tokens_per_expert == nullptr && (pb.num_experts != 1 || pb.dense_rows % BM != 0)) return MOK_ERR_INVALID_ARGUMENT;
+    if (pb.tokens_per_expert != nullptr && pb.num_tokens == nullptr) return MOK_ERR_INVALID_ARGUMENT;
+    return MOK_OK;
+}
+
+KernelParams base_params(const GemmProblem& pb) {
+    KernelParams kp{};
+    kp.tokens_per_expert = pb.tokens_per_expert;
+    kp.num_tokens = pb.num_tokens;
+    kp.num_experts = pb.num_experts;
+    kp.dense_rows = pb.dense_rows;
+    kp.row_begin = pb.row_begin;
+    kp.row_end = pb.row_end;
+    kp.n_sets = 1;
+    kp.k_sets = 1;
+    kp.status = pb.status;
+    return kp;
+}
+
+}  // namespace
+
+int launch_fp8_rows_gemm(const GemmProblem& pb, const Fp8Operand& A, int K, const Fp8Operand& B0, const Fp8Operand* B1,
+                         void* D0, void* D1, int N, cudaStream_t stream) {
+    int rc = check_problem(pb);
+    if (rc != MOK_OK) return rc;
+    if (K <= 0 || N <= 0 || K % BK != 0 || N % BN != 0) return MOK_ERR_INVALID_ARGUMENT;
+    MapSet ms0, ms1;
+    if ((rc = fill_set(&ms0, A, 1, B0, pb.num_experts)) != MOK_OK) return rc;
+    if ((rc = fill_set(&ms1, A, 1, B1 ? *B1 : B0, pb.num_experts)) != MOK_OK) return rc;
+    KernelParams kp = base_params(pb);
+    kp.n_blocks = N / BN;
+    kp.k_blocks = K / BK;
+    kp.n_sets = B1 ? 2 : 1;
+    kp.n_tiles_per_expert = N / 128;
+    kp.D0 = static_cast<bf16*>(D0);
+    kp.D1 = static_cast<bf16*>(D1);
+    kp.ldd = N;
+    return launch<MODE_ROWS>(ms0, ms1, kp, ((pb.row_end - pb.row_begin) / BM) * kp.n_blocks * kp.n_sets, stream);
+}
+
+int launch_fp8_rows_gemm_dual(const GemmProblem& pb, const Fp8Operand& A0, const Fp8Operand& A1, int K, const Fp8Operand& B0,
+                              const Fp8Operand& B1, void* D, int N, cudaStream_t stream) {
+    int rc = check_problem(pb);
+    if (rc != MOK_OK) return rc;
+    if (K <= 0 || N <= 0 || K % BK != 0 || N % BN != 0) return MOK_ERR_INVALID_ARGUMENT;
+    MapSet ms0, ms1;
+    if ((rc = fill_set(&ms0, A0, 1, B0, pb.num_experts)) != MOK_OK) return rc;
+    if ((rc = fill_set(&ms1, A1, 1, B1, pb.num_experts)) != MOK_OK) return rc;
+    KernelParams kp = base_params(pb);
+    kp.n_blocks = N / BN;
+    kp.k_blocks = K / BK;
+    kp.k_sets = 2;
+    kp.n_tiles_per_expert = N / 128;
+    kp.D0 = static_cast<bf16*>(D);
+    kp.ldd = N;
+    return launch<MODE_ROWS>(ms0, ms1, kp, ((pb.row_end - pb.row_begin) / BM) * kp.n_blocks, stream);
+}
+
+int launch_fp8_wgrad_gemm(const GemmProblem& pb, const Fp8Operand& At, int M, const Fp8Operand& Bt, int N, void* D,
+                          cudaStream_t stream) {
+    int rc = check_problem(pb);
+    if (rc != MOK_OK) return rc;
+    if (M <= 0 || N <= 0 || M % BM != 0 || N % BN != 0) return MOK_ERR_INVALID_ARGUMENT;
+    MapSet ms0;
+    if ((rc = fill_set(&ms0, At, 1, Bt, 1)) != MOK_OK) return rc;
+    KernelParams kp = base_params(pb);
+    kp.n_blocks = N / BN;
+    kp.m_blocks_w = M / BM;
+    kp.D0 = static_cast<bf16*>(D);
+    kp.ldd = N;
+    kp.d_expert_stride = static_cast<long long>(M) * N;
+    return launch<MODE_WGRAD>(ms0, ms0, kp, pb.num_experts * kp.m_blocks_w * kp.n_blocks, stream);
+}
+
+}  // namespace mok
+
+// ---------------------------------------------------------------------------------------------------------
+// C ABI: single launches, for tests and profiling
+// ---------------------------------------------------------------------------------------------------------
+static mok::Fp8Operand plain_operand(const void* data, const void* scales, long long rows, long long k) {
+    mok::Fp8Operand op;
+    op.data = data;
+    op.scales = scales;
+    op.ld = k;
+    op.rows = rows;
+    op.k_extent = k;
+    op.scale_row_tile_stride = (k / 128) * 512;
+    return op;
+}
+
+static mok::GemmProblem single_problem(const int32_t* tokens_per_expert, const int32_t* num_tokens, int num_experts, int rows,
+                                       uint32_t* status) {
+    mok::GemmProblem pb;
+    pb.tokens_per_expert = tokens_per_expert;
+    pb.num_tokens = num_tokens;
+    pb.num_experts = tokens_per_expert ? num_experts : 1;
+    pb.dense_rows = tokens_per_expert ? 0 : rows;
+    pb.row_begin = 0;
+    pb.row_end = rows;
+    pb.buffer_rows = rows;
+    pb.status = status;
+    return pb;
+}
+
+extern "C" int mok_grouped_gemm_mxfp8(const void* A_fp8, const void* A_sc, const void* B_fp8, const void* B_sc, void* D,
+                                      const int32_t* tokens_per_expert, const int32_t* num_tokens, int num_experts, int rows,
+                                      int N, int K, uint32_t* status, mok_stream_t stream) {
+    if (!A_fp8 || !A_sc || !B_fp8 || !B_sc || !D || rows <= 0 || rows % 256 != 0 || N <= 0 || K <= 0 || K % 128 != 0)
+        return MOK_ERR_INVALID_ARGUMENT;
+    const mok::GemmProblem pb = single_problem(tokens_per_expert, num_tokens, num_experts, rows, status);
+    const mok::Fp8Operand a = plain_operand(A_fp8, A_sc, rows, K);
+    const mok::Fp8Operand b = plain_operand(B_fp8, B_sc, static_cast<long long>(pb.num_experts) * N, K);
+    return mok::launch_fp8_rows_gemm(pb, a, K, b, nullptr, D, nullptr, N, reinterpret_cast<cudaStream_t>(stream));
+}
+
+extern "C" int mok_grouped_wgrad_mxfp8(const void* At_fp8, const void* At_sc, const void* Bt_fp8, const void* Bt_sc, void* D,
+                                       const int32_t* tokens_per_expert, const int32_t* num_tokens, int num_experts, int rows,
+                                       int M, int N, uint32_t* status, mok_stream_t stream) {
+    if (!At_fp8 || !At_sc || !Bt_fp8 || !Bt_sc || !D || rows <= 0 || rows % 256 != 0 || M <= 0 || N <= 0)
+        return MOK_ERR_INVALID_ARGUMENT;
+    const mok::GemmProblem pb = single_problem(tokens_per_expert, num_tokens, num_experts, rows, status);
+    const mok::Fp8Operand a = plain_operand(At_fp8, At_sc, M, rows);
+    const mok::Fp8Operand b = plain_operand(Bt_fp8, Bt_sc, N, rows);
+    return mok::launch_fp8_wgrad_gemm(pb, a, M, b, N, D, reinterpret_cast<cudaStream_t>(stream));
+}
