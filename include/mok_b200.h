@@ -179,6 +179,21 @@ typedef struct mok_layer_args {
     void *d_w_routed_gate, *d_w_routed_up, *d_w_routed_down;
     float* row_scratch;    /* fp32 [2 * MB]: router weight and router-weight gradient of every row (backward) */
     uint32_t* status;      /* uint32 [1] */
+    /* MXFP8 entry points only (NULL otherwise).  "fp8" = e4m3 bytes, "sc" = e8m0 scale tiles [rows/128, cols/128, 32, 16]
+     * of the matrix as stored (scales along its last dimension).  In the MXFP8 calls the bf16 routed activation
+     * fields above (x_routed ... d_x_routed) are scratch of the same shapes. */
+    const void *w_gate_fp8, *w_gate_sc, *w_up_fp8, *w_up_sc, *w_down_fp8, *w_down_sc;   /* [E,I,H] [E,I,H] [E,H,I] */
+    const void *w_gate_t_fp8, *w_gate_t_sc, *w_up_t_fp8, *w_up_t_sc;                     /* transposes [E,H,I] (backward) */
+    const void *w_down_t_fp8, *w_down_t_sc;                                              /* transpose [E,I,H] (backward) */
+    void *x_fp8, *x_sc;                             /* [MB,H] scratch */
+    void *x_fp8_t, *x_sc_t;                         /* [H,MB] saved context */
+    void *gate_fp8, *gate_sc, *up_fp8, *up_sc;      /* [MB,I] saved context */
+    void *hidden_fp8, *hidden_sc;                   /* [MB,I] scratch */
+    void *hidden_fp8_t, *hidden_sc_t;               /* [I,MB] saved context */
+    void *d_y_fp8, *d_y_sc;                         /* [MB,H] backward out */
+    void *d_y_fp8_t, *d_y_sc_t;                     /* [H,MB] scratch */
+    void *d_gate_fp8, *d_gate_sc, *d_up_fp8, *d_up_sc;              /* [MB,I] backward out */
+    void *d_gate_fp8_t, *d_gate_sc_t, *d_up_fp8_t, *d_up_sc_t;      /* [I,MB] scratch */
 } mok_layer_args;
 
 /*
@@ -200,6 +215,19 @@ int mok_moe_recompute_bf16(const mok_layer_args* args, mok_stream_t stream);
  * including zero_empty_routed_wgrads (csrc/utils.cuh:301-322).
  */
 int mok_moe_backward_bf16(const mok_layer_args* args, mok_stream_t stream);
+
+/*
+ * MXFP8 forward / context recomputation / backward: routed experts in e4m3 with e8m0 scales per 32 elements along K
+ * (block-scaled tensor-core MMA), shared expert in bf16.  Activations are quantized where the reference quantizes
+ * them: x after dispatch (normal for the gate/up GEMM, transposed for wgrad), gate and up after their GEMM (saved for
+ * backward), hidden after SwiGLU (normal for the down GEMM, transposed for wgrad), d_y*w after dispatch, d_gate / d_up
+ * after SwiGLU backward.  Replace: dispatch_mlp_swiglu_combine_fwd_mxfp8 (csrc/megakernel/forward.cuh:293-428,
+ * op mok/ops.py:200-374), recompute_forward_context_mxfp8 (op mok/ops.py:523-665),
+ * dispatch_mlp_swiglu_combine_bwd_mxfp8 (csrc/megakernel/backward.cuh:681-873, op mok/ops.py:785-1076).
+ */
+int mok_moe_forward_mxfp8(const mok_layer_args* args, mok_stream_t stream);
+int mok_moe_recompute_mxfp8(const mok_layer_args* args, mok_stream_t stream);
+int mok_moe_backward_mxfp8(const mok_layer_args* args, mok_stream_t stream);
 
 /*
  * One grouped GEMM launch, exposed for tests and profiling.  D[rows, N] = A[rows, K] * B[e]^T with rows grouped

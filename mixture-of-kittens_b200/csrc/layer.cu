@@ -19,6 +19,8 @@
 #include "comm.cuh"
 #include "elementwise.cuh"
 #include "grouped_gemm.cuh"
+#include "mxfp8.cuh"
+#include "mxfp8_gemm.cuh"
 
 namespace mok {
 namespace {
@@ -88,7 +90,7 @@ int chunk_rows_for(const mok_layer_args* a) {
     return rows < min_rows ? min_rows : rows;
 }
 
-int check_common(const mok_layer_args* a) {
+int check_common(const mok_layer_args* a, bool fp8 = false) {
     if (a == nullptr) return MOK_ERR_INVALID_ARGUMENT;
     if (a->ep_size < 1 || a->ep_size > MOK_MAX_EP || a->rank < 0 || a->rank >= a->ep_size) return MOK_ERR_INVALID_ARGUMENT;
     if (a->num_local_tokens <= 0 || a->num_local_tokens % 256 != 0) return MOK_ERR_INVALID_ARGUMENT;
@@ -102,7 +104,8 @@ int check_common(const mok_layer_args* a) {
     if (a->macrobatch_size <= 0 || a->macrobatch_size % a->minibatch_size != 0) return MOK_ERR_INVALID_ARGUMENT;
     if (a->num_comm_sms <= 0) return MOK_ERR_INVALID_ARGUMENT;
     if (!a->peer_rank || !a->peer_token_idx || !a->num_tokens || !a->tokens_per_expert) return MOK_ERR_INVALID_ARGUMENT;
-    if (!a->x_ptrs || !a->x_local || !a->w_routed_gate || !a->w_routed_up) return MOK_ERR_INVALID_ARGUMENT;
+    if (!a->x_ptrs || !a->x_local) return MOK_ERR_INVALID_ARGUMENT;
+    if (!fp8 && (!a->w_routed_gate || !a->w_routed_up)) return MOK_ERR_INVALID_ARGUMENT;
     if (!a->x_routed || !a->gate_routed || !a->up_routed || !a->hidden_routed) return MOK_ERR_INVALID_ARGUMENT;
     const bool any_shared = a->w_shared_gate || a->w_shared_up;
     if (any_shared && !(a->w_shared_gate && a->w_shared_up && a->gate_shared && a->up_shared && a->hidden_shared))
@@ -192,6 +195,101 @@ int shared_up_to_hidden(const mok_layer_args* a, cudaStream_t s) {
                              a->intermediate, false, s));
     MOK_TRY(launch_swiglu_fwd(a->gate_shared, a->up_shared, a->hidden_shared, nullptr, a->num_local_tokens, 0,
                               a->num_local_tokens, a->intermediate, a->has_swiglu_limit != 0, a->swiglu_limit, s));
+    return MOK_OK;
+}
+
+// bf16 backward of the shared expert (dense over this rank's tokens)
+int shared_backward(const mok_layer_args* a, cudaStream_t s) {
+    const int H = a->hidden, I = a->intermediate, T = a->num_local_tokens;
+    const GemmProblem p = shared_problem(a);
+    const void* d_y = a->d_y_local;
+    const void* x = a->x_local;
+    // d_hidden = d_y * Wd   (Wd is [H, I]: K = H, N = I)
+    MOK_TRY(launch_rows_gemm(p, d_y, H, a->w_shared_down, nullptr, a->d_hidden_shared, nullptr, I, true, s));
+    MOK_TRY(launch_swiglu_bwd(a->gate_shared, a->up_shared, a->d_hidden_shared, a->d_gate_shared, a->d_up_shared, nullptr, T, 0,
+                              T, I, a->has_swiglu_limit != 0, a->swiglu_limit, nullptr, nullptr, s));
+    // d_x = d_gate * Wg + d_up * Wu   (W is [I, H]: K = I, N = H)
+    MOK_TRY(launch_rows_gemm_dual(p, a->d_gate_shared, a->d_up_shared, I, a->w_shared_gate, a->w_shared_up, a->d_x_shared, H, s));
+    MOK_TRY(launch_wgrad_gemm(p, d_y, H, a->hidden_shared, I, a->d_w_shared_down, s));
+    MOK_TRY(launch_wgrad_gemm(p, a->d_gate_shared, I, x, H, a->d_w_shared_gate, s));
+    MOK_TRY(launch_wgrad_gemm(p, a->d_up_shared, I, x, H, a->d_w_shared_up, s));
+    return MOK_OK;
+}
+
+// ---- MXFP8 operands ----------------------------------------------------------------------------------------------
+long long scale_tile_row_bytes(long long cols) { return (cols / 128) * 512; }
+
+// rows [s.begin, ...) of a row-major [MB, cols] e4m3 activation buffer
+Fp8Operand act_rows(const mok_layer_args* a, const void* data, const void* sc, int cols, const Span& s) {
+    const long long off = s.begin - s.base;
+    Fp8Operand op;
+    op.data = static_cast<const uint8_t*>(data) + off * cols;
+    op.scales = static_cast<const uint8_t*>(sc) + (off / 128) * scale_tile_row_bytes(cols);
+    op.ld = cols;
+    op.rows = a->macrobatch_size - off;
+    op.k_extent = cols;
+    op.scale_row_tile_stride = scale_tile_row_bytes(cols);
+    return op;
+}
+
+// a transposed [cols, MB] e4m3 activation buffer (K = schedule rows of the window)
+Fp8Operand act_transposed(const mok_layer_args* a, const void* data, const void* sc, int cols) {
+    Fp8Operand op;
+    op.data = data;
+    op.scales = sc;
+    op.ld = a->macrobatch_size;
+    op.rows = cols;
+    op.k_extent = a->macrobatch_size;
+    op.scale_row_tile_stride = scale_tile_row_bytes(a->macrobatch_size);
+    return op;
+}
+
+// expert weights [E, n, k]
+Fp8Operand weight_operand(const mok_layer_args* a, const void* data, const void* sc, int n, int k) {
+    Fp8Operand op;
+    op.data = data;
+    op.scales = sc;
+    op.ld = k;
+    op.rows = static_cast<long long>(a->num_local_experts) * n;
+    op.k_extent = k;
+    op.scale_row_tile_stride = scale_tile_row_bytes(k);
+    return op;
+}
+
+// quantize span rows of a bf16 [MB, cols] buffer into the normal and / or transposed e4m3 buffers
+int quantize_span(const mok_layer_args* a, const Span& s, const void* src, int cols, void* q, void* sc, void* qt, void* sct,
+                  cudaStream_t st) {
+    const long long off = s.begin - s.base;
+    uint8_t* q_ = q ? static_cast<uint8_t*>(q) + off * cols : nullptr;
+    uint8_t* sc_ = sc ? static_cast<uint8_t*>(sc) + (off / 128) * scale_tile_row_bytes(cols) : nullptr;
+    uint8_t* qt_ = qt ? static_cast<uint8_t*>(qt) + off : nullptr;
+    uint8_t* sct_ = sct ? static_cast<uint8_t*>(sct) + (off / 128) * 512 : nullptr;
+    return launch_quantize_rows(rows_bf16(src, s, cols), cols, a->num_tokens, s.begin, s.end, q_, sc_, scale_tile_row_bytes(cols),
+                                qt_, a->macrobatch_size, sct_, scale_tile_row_bytes(a->macrobatch_size), st);
+}
+
+// x (bf16, dispatched) -> x_fp8 (+ transpose) -> gate, up (bf16 scratch + saved e4m3) -> hidden (bf16 scratch, e4m3 + transpose)
+int gate_up_hidden_mxfp8(const mok_layer_args* a, const Span& s, cudaStream_t st) {
+    const int H = a->hidden, I = a->intermediate;
+    MOK_TRY(quantize_span(a, s, a->x_routed, H, a->x_fp8, a->x_sc, a->x_fp8_t, a->x_sc_t, st));
+    const Fp8Operand wg = weight_operand(a, a->w_gate_fp8, a->w_gate_sc, I, H);
+    const Fp8Operand wu = weight_operand(a, a->w_up_fp8, a->w_up_sc, I, H);
+    MOK_TRY(launch_fp8_rows_gemm(routed_problem(a, s), act_rows(a, a->x_fp8, a->x_sc, H, s), H, wg, &wu,
+                                 rows_bf16(a->gate_routed, s, I), rows_bf16(a->up_routed, s, I), I, st));
+    MOK_TRY(quantize_span(a, s, a->gate_routed, I, a->gate_fp8, a->gate_sc, nullptr, nullptr, st));
+    MOK_TRY(quantize_span(a, s, a->up_routed, I, a->up_fp8, a->up_sc, nullptr, nullptr, st));
+    MOK_TRY(launch_swiglu_fwd(rows_bf16(a->gate_routed, s, I), rows_bf16(a->up_routed, s, I), rows_bf16(a->hidden_routed, s, I),
+                              a->num_tokens, 0, s.begin, s.end, I, a->has_swiglu_limit != 0, a->swiglu_limit, st));
+    MOK_TRY(quantize_span(a, s, a->hidden_routed, I, a->hidden_fp8, a->hidden_sc, a->hidden_fp8_t, a->hidden_sc_t, st));
+    return MOK_OK;
+}
+
+int check_mxfp8_forward_fields(const mok_layer_args* a) {
+    if (!a->w_gate_fp8 || !a->w_gate_sc || !a->w_up_fp8 || !a->w_up_sc) return MOK_ERR_INVALID_ARGUMENT;
+    if (!a->x_fp8 || !a->x_sc || !a->x_fp8_t || !a->x_sc_t || !a->gate_fp8 || !a->gate_sc || !a->up_fp8 || !a->up_sc ||
+        !a->hidden_fp8 || !a->hidden_sc || !a->hidden_fp8_t || !a->hidden_sc_t)
+        return MOK_ERR_INVALID_ARGUMENT;
+    if (a->macrobatch_size % 256 != 0) return MOK_ERR_INVALID_ARGUMENT;
     return MOK_OK;
 }
 
@@ -322,20 +420,7 @@ extern "C" int mok_moe_backward_bf16(const mok_layer_args* a, mok_stream_t strea
         MOK_TRY(order_after(d, s, d->comm));
     }
 
-    if (shared) {
-        const GemmProblem p = shared_problem(a);
-        const void* d_y = a->d_y_local;
-        const void* x = a->x_local;
-        // d_hidden = d_y * Wd   (Wd is [H, I]: K = H, N = I)
-        MOK_TRY(launch_rows_gemm(p, d_y, H, a->w_shared_down, nullptr, a->d_hidden_shared, nullptr, I, true, s));
-        MOK_TRY(launch_swiglu_bwd(a->gate_shared, a->up_shared, a->d_hidden_shared, a->d_gate_shared, a->d_up_shared, nullptr,
-                                  T, 0, T, I, clamp, a->swiglu_limit, nullptr, nullptr, s));
-        // d_x = d_gate * Wg + d_up * Wu   (W is [I, H]: K = I, N = H)
-        MOK_TRY(launch_rows_gemm_dual(p, a->d_gate_shared, a->d_up_shared, I, a->w_shared_gate, a->w_shared_up, a->d_x_shared, H, s));
-        MOK_TRY(launch_wgrad_gemm(p, d_y, H, a->hidden_shared, I, a->d_w_shared_down, s));
-        MOK_TRY(launch_wgrad_gemm(p, a->d_gate_shared, I, x, H, a->d_w_shared_gate, s));
-        MOK_TRY(launch_wgrad_gemm(p, a->d_up_shared, I, x, H, a->d_w_shared_up, s));
-    }
+    if (shared) MOK_TRY(shared_backward(a, s));
 
     float* row_weight = a->row_scratch;
     float* row_grad = a->row_scratch + a->macrobatch_size;
@@ -371,6 +456,153 @@ extern "C" int mok_moe_backward_bf16(const mok_layer_args* a, mok_stream_t strea
         MOK_TRY(launch_wgrad_gemm(p, a->d_y_routed, H, a->hidden_routed, I, a->d_w_routed_down, s));
         MOK_TRY(launch_wgrad_gemm(p, a->d_gate_routed, I, a->x_routed, H, a->d_w_routed_gate, s));
         MOK_TRY(launch_wgrad_gemm(p, a->d_up_routed, I, a->x_routed, H, a->d_w_routed_up, s));
+        if (overlapped) {
+            MOK_TRY(order_after(d, d->comm, s));
+            if (wi + 1 < num_windows(a)) MOK_TRY(order_after(d, s, d->comm));
+        }
+    }
+    MOK_TRY(launch_zero_empty_wgrads(a->tokens_per_expert, a->num_local_experts, a->d_w_routed_gate, a->d_w_routed_up,
+                                     a->d_w_routed_down, static_cast<long long>(H) * I, s));
+    return MOK_OK;
+}
+
+// ---------------------------------------------------------------------------------------------------------------------
+// MXFP8 entry points: same launch structure, routed GEMMs block-scaled, activations quantized between the steps
+// ---------------------------------------------------------------------------------------------------------------------
+extern "C" int mok_moe_forward_mxfp8(const mok_layer_args* a, mok_stream_t stream) {
+    using namespace mok;
+    MOK_TRY(check_common(a, true));
+    MOK_TRY(check_mxfp8_forward_fields(a));
+    if (!a->combine_ptrs || !a->w_down_fp8 || !a->w_down_sc || !a->y_routed) return MOK_ERR_INVALID_ARGUMENT;
+    if (a->w_shared_gate && (!a->w_shared_down || !a->y_shared)) return MOK_ERR_INVALID_ARGUMENT;
+    cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+    const bool overlapped = overlap_enabled();
+    DeviceStreams* d = nullptr;
+    if (overlapped) {
+        MOK_TRY(streams_for_current_device(&d));
+        MOK_TRY(order_after(d, s, d->comm));
+    }
+    const int H = a->hidden, I = a->intermediate;
+    if (a->w_shared_gate) {
+        MOK_TRY(shared_up_to_hidden(a, s));
+        MOK_TRY(launch_rows_gemm(shared_problem(a), a->hidden_shared, I, a->w_shared_down, nullptr, a->y_shared, nullptr, H,
+                                 false, s));
+    }
+    const Fp8Operand wd = weight_operand(a, a->w_down_fp8, a->w_down_sc, H, I);
+    for (int wi = num_windows(a) - 1; wi >= 0; --wi) {
+        const Span win = window_span(a, wi);
+        MOK_TRY(run_chunks(
+            a, win, overlapped, d, s,
+            [&](const Span& c, int ctas, cudaStream_t st) { return dispatch_x(a, c, ctas, st); },
+            [&](const Span& c, cudaStream_t st) {
+                MOK_TRY(gate_up_hidden_mxfp8(a, c, st));
+                return launch_fp8_rows_gemm(routed_problem(a, c), act_rows(a, a->hidden_fp8, a->hidden_sc, I, c), I, wd, nullptr,
+                                            rows_bf16(a->y_routed, c, H), nullptr, H, st);
+            },
+            [&](const Span& c, int ctas, cudaStream_t st) {
+                return launch_combine(a->combine_ptrs, nullptr, a->ep_size, rows_of(a, c), a->topk, a->num_local_tokens, H,
+                                      rows_bf16(a->y_routed, c, H), nullptr, ctas, st);
+            }));
+        if (overlapped) {
+            MOK_TRY(order_after(d, d->comm, s));
+            if (wi > 0) MOK_TRY(order_after(d, s, d->comm));
+        }
+    }
+    return MOK_OK;
+}
+
+extern "C" int mok_moe_recompute_mxfp8(const mok_layer_args* a, mok_stream_t stream) {
+    using namespace mok;
+    MOK_TRY(check_common(a, true));
+    MOK_TRY(check_mxfp8_forward_fields(a));
+    cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+    if (a->w_shared_gate) MOK_TRY(shared_up_to_hidden(a, s));
+    const Span win = window_span(a, 0);
+    MOK_TRY(dispatch_x(a, win, 0, s));
+    MOK_TRY(gate_up_hidden_mxfp8(a, win, s));
+    return MOK_OK;
+}
+
+extern "C" int mok_moe_backward_mxfp8(const mok_layer_args* a, mok_stream_t stream) {
+    using namespace mok;
+    MOK_TRY(check_common(a, true));
+    MOK_TRY(check_mxfp8_forward_fields(a));
+    if (!a->d_y_ptrs || !a->d_x_routed_ptrs || !a->router_weight_ptrs || !a->d_router_weight_ptrs) return MOK_ERR_INVALID_ARGUMENT;
+    if (!a->w_gate_t_fp8 || !a->w_gate_t_sc || !a->w_up_t_fp8 || !a->w_up_t_sc || !a->w_down_t_fp8 || !a->w_down_t_sc)
+        return MOK_ERR_INVALID_ARGUMENT;
+    if (!a->d_x_routed || !a->d_gate_routed || !a->d_up_routed || !a->d_hidden_routed || !a->d_y_routed || !a->d_w_routed_gate ||
+        !a->d_w_routed_up || !a->d_w_routed_down || !a->row_scratch)
+        return MOK_ERR_INVALID_ARGUMENT;
+    if (!a->d_y_fp8 || !a->d_y_sc || !a->d_y_fp8_t || !a->d_y_sc_t || !a->d_gate_fp8 || !a->d_gate_sc || !a->d_up_fp8 ||
+        !a->d_up_sc || !a->d_gate_fp8_t || !a->d_gate_sc_t || !a->d_up_fp8_t || !a->d_up_sc_t)
+        return MOK_ERR_INVALID_ARGUMENT;
+    const bool shared = a->w_shared_gate != nullptr;
+    if (shared && !(a->d_y_local && a->w_shared_down && a->d_x_shared && a->d_gate_shared && a->d_up_shared && a->d_hidden_shared &&
+                    a->d_w_shared_gate && a->d_w_shared_up && a->d_w_shared_down))
+        return MOK_ERR_INVALID_ARGUMENT;
+    cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+    const int H = a->hidden, I = a->intermediate, T = a->num_local_tokens;
+    const bool clamp = a->has_swiglu_limit != 0;
+    const bool overlapped = overlap_enabled();
+    DeviceStreams* d = nullptr;
+    if (overlapped) {
+        MOK_TRY(streams_for_current_device(&d));
+        MOK_TRY(order_after(d, s, d->comm));
+    }
+    if (shared) MOK_TRY(shared_backward(a, s));
+
+    const Fp8Operand wd_t = weight_operand(a, a->w_down_t_fp8, a->w_down_t_sc, I, H);   // [E, I, H]: N = I, K = H
+    const Fp8Operand wg_t = weight_operand(a, a->w_gate_t_fp8, a->w_gate_t_sc, H, I);   // [E, H, I]: N = H, K = I
+    const Fp8Operand wu_t = weight_operand(a, a->w_up_t_fp8, a->w_up_t_sc, H, I);
+    float* row_weight = a->row_scratch;
+    float* row_grad = a->row_scratch + a->macrobatch_size;
+    const long long sc_I = scale_tile_row_bytes(I);
+    for (int wi = 0; wi < num_windows(a); ++wi) {
+        const Span win = window_span(a, wi);
+        if (wi > 0) {
+            MOK_TRY(dispatch_x(a, win, 0, s));
+            MOK_TRY(gate_up_hidden_mxfp8(a, win, s));
+        }
+        MOK_TRY(run_chunks(
+            a, win, overlapped, d, s,
+            [&](const Span& c, int ctas, cudaStream_t st) {
+                return launch_dispatch(a->d_y_ptrs, a->router_weight_ptrs, a->ep_size, rows_of(a, c), a->topk, T, H,
+                                       rows_bf16(a->d_y_routed, c, H), at_row(row_weight, c, 1), ctas, st);
+            },
+            [&](const Span& c, cudaStream_t st) {
+                const GemmProblem p = routed_problem(a, c);
+                const long long off = c.begin - c.base;
+                MOK_TRY(quantize_span(a, c, a->d_y_routed, H, a->d_y_fp8, a->d_y_sc, a->d_y_fp8_t, a->d_y_sc_t, st));
+                MOK_TRY(launch_fp8_rows_gemm(p, act_rows(a, a->d_y_fp8, a->d_y_sc, H, c), H, wd_t, nullptr,
+                                             rows_bf16(a->d_hidden_routed, c, I), nullptr, I, st));
+                // the saved gate / up are e4m3: expand them (exactly) into the bf16 scratch the SwiGLU backward reads
+                MOK_TRY(launch_dequantize_rows(static_cast<const uint8_t*>(a->gate_fp8) + off * I,
+                                               static_cast<const uint8_t*>(a->gate_sc) + (off / 128) * sc_I, sc_I,
+                                               rows_bf16(a->gate_routed, c, I), I, a->num_tokens, c.begin, c.end, st));
+                MOK_TRY(launch_dequantize_rows(static_cast<const uint8_t*>(a->up_fp8) + off * I,
+                                               static_cast<const uint8_t*>(a->up_sc) + (off / 128) * sc_I, sc_I,
+                                               rows_bf16(a->up_routed, c, I), I, a->num_tokens, c.begin, c.end, st));
+                MOK_TRY(launch_swiglu_bwd(rows_bf16(a->gate_routed, c, I), rows_bf16(a->up_routed, c, I),
+                                          rows_bf16(a->d_hidden_routed, c, I), rows_bf16(a->d_gate_routed, c, I),
+                                          rows_bf16(a->d_up_routed, c, I), a->num_tokens, 0, c.begin, c.end, I, clamp,
+                                          a->swiglu_limit, at_row(row_weight, c, 1), at_row(row_grad, c, 1), st));
+                MOK_TRY(quantize_span(a, c, a->d_gate_routed, I, a->d_gate_fp8, a->d_gate_sc, a->d_gate_fp8_t, a->d_gate_sc_t, st));
+                MOK_TRY(quantize_span(a, c, a->d_up_routed, I, a->d_up_fp8, a->d_up_sc, a->d_up_fp8_t, a->d_up_sc_t, st));
+                return launch_fp8_rows_gemm_dual(p, act_rows(a, a->d_gate_fp8, a->d_gate_sc, I, c),
+                                                 act_rows(a, a->d_up_fp8, a->d_up_sc, I, c), I, wg_t, wu_t,
+                                                 rows_bf16(a->d_x_routed, c, H), H, st);
+            },
+            [&](const Span& c, int ctas, cudaStream_t st) {
+                return launch_combine(a->d_x_routed_ptrs, a->d_router_weight_ptrs, a->ep_size, rows_of(a, c), a->topk, T, H,
+                                      rows_bf16(a->d_x_routed, c, H), at_row(row_grad, c, 1), ctas, st);
+            }));
+        const GemmProblem p = routed_problem(a, win);
+        MOK_TRY(launch_fp8_wgrad_gemm(p, act_transposed(a, a->d_y_fp8_t, a->d_y_sc_t, H), H,
+                                      act_transposed(a, a->hidden_fp8_t, a->hidden_sc_t, I), I, a->d_w_routed_down, s));
+        MOK_TRY(launch_fp8_wgrad_gemm(p, act_transposed(a, a->d_gate_fp8_t, a->d_gate_sc_t, I), I,
+                                      act_transposed(a, a->x_fp8_t, a->x_sc_t, H), H, a->d_w_routed_gate, s));
+        MOK_TRY(launch_fp8_wgrad_gemm(p, act_transposed(a, a->d_up_fp8_t, a->d_up_sc_t, I), I,
+                                      act_transposed(a, a->x_fp8_t, a->x_sc_t, H), H, a->d_w_routed_up, s));
         if (overlapped) {
             MOK_TRY(order_after(d, d->comm, s));
             if (wi + 1 < num_windows(a)) MOK_TRY(order_after(d, s, d->comm));

@@ -6,6 +6,10 @@
 // 1e-12) rounded UP to a power of two (cvt.rp.satfinite.ue8m0x2), elements multiplied by the exact reciprocal
 // 2^(127-e) and converted with cvt.rn.satfinite.e4m3x2.  Scale bytes are stored in the tensor-core scale-factor
 // layout: tile [rows/128][cols/128] of 512 bytes, byte (r % 32) * 16 + (r / 32) * 4 + kblock (csrc/mxfp8.cuh:181-184).
+//
+// The same kernel serves the stand-alone op (whole matrices) and the fused layer (a window of schedule rows of an
+// activation buffer, limited on the device by the padded token count; the transposed output then is a column range
+// of a wider [cols, buffer_rows] matrix).
 #include "mxfp8.cuh"
 
 namespace mok {
@@ -14,26 +18,41 @@ namespace {
 constexpr int kTile = 128;
 constexpr int kRowPitch = kTile * 2 + 16;   // bytes; the 16-byte pad keeps row-wise 16 B reads conflict free
 
-__global__ void __launch_bounds__(128) quantize_kernel(const bf16* __restrict__ x, int rows, int cols, uint8_t* __restrict__ q,
-                                                        uint8_t* __restrict__ sc, uint8_t* __restrict__ qt,
-                                                        uint8_t* __restrict__ sct) {
+struct QuantArgs {
+    const bf16* x;             // row 0 of the span / matrix 0
+    long long x_ld;            // elements between rows
+    long long x_mat_stride;    // elements between matrices (blockIdx.z)
+    uint8_t* q;                // normal output, same shape as x
+    long long q_mat_stride;
+    uint8_t* sc;               // scale tile (row tile 0, col tile 0)
+    long long sc_row_tile_stride, sc_mat_stride;   // bytes
+    uint8_t* qt;               // transposed output: element (c, r) at qt[c * qt_ld + r]
+    long long qt_ld, qt_mat_stride;
+    uint8_t* sct;              // scale tile (col tile 0, row tile 0) of the transposed output
+    long long sct_row_tile_stride, sct_mat_stride;
+    const int* num_tokens;     // optional device row limit (schedule rows)
+    int row_begin, row_end;    // schedule rows covered by the span (row_end also bounds a dense matrix)
+};
+
+__global__ void __launch_bounds__(128) quantize_kernel(const QuantArgs a) {
     __shared__ __align__(16) uint8_t tile[kTile * kRowPitch];
     const int tid = threadIdx.x;
     const int tc = blockIdx.x, tr = blockIdx.y, e = blockIdx.z;
-    const bf16* src = x + (static_cast<size_t>(e) * rows + static_cast<size_t>(tr) * kTile) * cols + static_cast<size_t>(tc) * kTile;
+    const int limit = a.num_tokens != nullptr ? min(a.row_end, *a.num_tokens) : a.row_end;
+    if (a.row_begin + tr * kTile >= limit) return;
+    const bf16* src = a.x + e * a.x_mat_stride + static_cast<long long>(tr) * kTile * a.x_ld + static_cast<long long>(tc) * kTile;
 
-    // 128 rows x 16 vectors of 16 bytes, coalesced along the row
 #pragma unroll 4
-    for (int i = tid; i < kTile * 16; i += 128) {
+    for (int i = tid; i < kTile * 16; i += 128) {   // 128 rows x 16 vectors of 16 bytes, coalesced along the row
         const int r = i >> 4, v = i & 15;
-        const uint4 val = *reinterpret_cast<const uint4*>(src + static_cast<size_t>(r) * cols + v * 8);
+        const uint4 val = *reinterpret_cast<const uint4*>(src + static_cast<long long>(r) * a.x_ld + v * 8);
         *reinterpret_cast<uint4*>(tile + r * kRowPitch + v * 16) = val;
     }
     __syncthreads();
 
-    if (q != nullptr) {   // thread = row of the tile, four blocks of 32 along the row
+    if (a.q != nullptr) {   // thread = row of the tile, four blocks of 32 along the row
         uint32_t scale_word = 0;
-        uint8_t* out = q + (static_cast<size_t>(e) * rows + static_cast<size_t>(tr) * kTile + tid) * cols + static_cast<size_t>(tc) * kTile;
+        uint8_t* out = a.q + e * a.q_mat_stride + (static_cast<long long>(tr) * kTile + tid) * a.x_ld + static_cast<long long>(tc) * kTile;
 #pragma unroll
         for (int kb = 0; kb < 4; ++kb) {
             uint32_t packed[16];
@@ -48,12 +67,12 @@ __global__ void __launch_bounds__(128) quantize_kernel(const bf16* __restrict__ 
             *reinterpret_cast<uint4*>(out + kb * 32) = make_uint4(out8[0], out8[1], out8[2], out8[3]);
             *reinterpret_cast<uint4*>(out + kb * 32 + 16) = make_uint4(out8[4], out8[5], out8[6], out8[7]);
         }
-        uint8_t* sdst = sc + ((static_cast<size_t>(e) * (rows / kTile) + tr) * (cols / kTile) + tc) * 512;
+        uint8_t* sdst = a.sc + e * a.sc_mat_stride + tr * a.sc_row_tile_stride + static_cast<long long>(tc) * 512;
         *reinterpret_cast<uint32_t*>(sdst + (tid & 31) * 16 + (tid >> 5) * 4) = scale_word;
     }
-    if (qt != nullptr) {  // thread = column of the tile = row of the transpose, four blocks of 32 down the column
+    if (a.qt != nullptr) {  // thread = column of the tile = row of the transpose, four blocks of 32 down the column
         uint32_t scale_word = 0;
-        uint8_t* out = qt + (static_cast<size_t>(e) * cols + static_cast<size_t>(tc) * kTile + tid) * rows + static_cast<size_t>(tr) * kTile;
+        uint8_t* out = a.qt + e * a.qt_mat_stride + (static_cast<long long>(tc) * kTile + tid) * a.qt_ld + static_cast<long long>(tr) * kTile;
 #pragma unroll
         for (int kb = 0; kb < 4; ++kb) {
             uint32_t packed[16];
@@ -69,12 +88,90 @@ __global__ void __launch_bounds__(128) quantize_kernel(const bf16* __restrict__ 
             *reinterpret_cast<uint4*>(out + kb * 32) = make_uint4(out8[0], out8[1], out8[2], out8[3]);
             *reinterpret_cast<uint4*>(out + kb * 32 + 16) = make_uint4(out8[4], out8[5], out8[6], out8[7]);
         }
-        uint8_t* sdst = sct + ((static_cast<size_t>(e) * (cols / kTile) + tc) * (rows / kTile) + tr) * 512;
+        uint8_t* sdst = a.sct + e * a.sct_mat_stride + tc * a.sct_row_tile_stride + static_cast<long long>(tr) * 512;
         *reinterpret_cast<uint32_t*>(sdst + (tid & 31) * 16 + (tid >> 5) * 4) = scale_word;
     }
 }
 
+// bf16[r, c] = e4m3[r, c] * 2^(scale(r, c / 32) - 127); exact (3 mantissa bits fit bf16).  One thread per 16 elements.
+__global__ void __launch_bounds__(256) dequantize_kernel(const uint8_t* __restrict__ q, const uint8_t* __restrict__ sc,
+                                                          long long sc_row_tile_stride, bf16* __restrict__ out, int cols,
+                                                          const int* __restrict__ num_tokens, int row_begin, int row_end) {
+    const int limit = num_tokens != nullptr ? min(row_end, *num_tokens) : row_end;
+    const long long rows = limit - row_begin;
+    const int vec_per_row = cols / 16;
+    const long long n = rows * vec_per_row;
+    const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+    for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride) {
+        const long long r = i / vec_per_row;
+        const int c = static_cast<int>(i - r * vec_per_row) * 16;
+        const uint4 v = *reinterpret_cast<const uint4*>(q + r * cols + c);
+        const int rr = static_cast<int>(r & 127);
+        const uint8_t sbyte = sc[(r >> 7) * sc_row_tile_stride + static_cast<long long>(c >> 7) * 512 + (rr & 31) * 16 + (rr >> 5) * 4 +
+                                 ((c & 127) >> 5)];
+        const float scale = __uint_as_float(static_cast<uint32_t>(sbyte) << 23);
+        const uint32_t words[4] = {v.x, v.y, v.z, v.w};
+        uint32_t o[8];
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                const __half2_raw hr = __nv_cvt_fp8x2_to_halfraw2(static_cast<__nv_fp8x2_storage_t>(words[w] >> (16 * h)), __NV_E4M3);
+                const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&hr));
+                o[w * 2 + h] = pack_bf16x2(f.x * scale, f.y * scale);
+            }
+        }
+        uint4* dst = reinterpret_cast<uint4*>(out + r * cols + c);
+        dst[0] = make_uint4(o[0], o[1], o[2], o[3]);
+        dst[1] = make_uint4(o[4], o[5], o[6], o[7]);
+    }
+}
+
 }  // namespace
+
+int launch_quantize_rows(const void* x, int cols, const int32_t* num_tokens, int row_begin, int row_end, void* q, void* sc,
+                         long long sc_row_tile_stride, void* qt, long long qt_ld, void* sct, long long sct_row_tile_stride,
+                         cudaStream_t stream) {
+    if (x == nullptr || cols <= 0 || cols % 128 != 0 || row_end <= row_begin || (row_end - row_begin) % 128 != 0)
+        return MOK_ERR_INVALID_ARGUMENT;
+    if ((q == nullptr) != (sc == nullptr) || (qt == nullptr) != (sct == nullptr) || (q == nullptr && qt == nullptr))
+        return MOK_ERR_INVALID_ARGUMENT;
+    QuantArgs a{};
+    a.x = static_cast<const bf16*>(x);
+    a.x_ld = cols;
+    a.q = static_cast<uint8_t*>(q);
+    a.sc = static_cast<uint8_t*>(sc);
+    a.sc_row_tile_stride = sc_row_tile_stride;
+    a.qt = static_cast<uint8_t*>(qt);
+    a.qt_ld = qt_ld;
+    a.sct = static_cast<uint8_t*>(sct);
+    a.sct_row_tile_stride = sct_row_tile_stride;
+    a.num_tokens = num_tokens;
+    a.row_begin = row_begin;
+    a.row_end = row_end;
+    const int row_tiles = (row_end - row_begin) / 128;
+    if (row_tiles > 65535) return MOK_ERR_TOO_LARGE;
+    dim3 grid(cols / 128, row_tiles, 1);
+    quantize_kernel<<<grid, 128, 0, stream>>>(a);
+    MOK_LAUNCH_CHECK("mxfp8_quantize_kernel");
+    return MOK_OK;
+}
+
+int launch_dequantize_rows(const void* q, const void* sc, long long sc_row_tile_stride, void* out, int cols,
+                           const int32_t* num_tokens, int row_begin, int row_end, cudaStream_t stream) {
+    if (q == nullptr || sc == nullptr || out == nullptr || cols <= 0 || cols % 128 != 0 || row_end <= row_begin)
+        return MOK_ERR_INVALID_ARGUMENT;
+    const long long items = static_cast<long long>(row_end - row_begin) * (cols / 16);
+    long long blocks = (items + 255) / 256;
+    const long long cap = static_cast<long long>(sm_count()) * 16;
+    if (blocks > cap) blocks = cap;
+    dequantize_kernel<<<static_cast<int>(blocks), 256, 0, stream>>>(static_cast<const uint8_t*>(q), static_cast<const uint8_t*>(sc),
+                                                                    sc_row_tile_stride, static_cast<bf16*>(out), cols, num_tokens,
+                                                                    row_begin, row_end);
+    MOK_LAUNCH_CHECK("mxfp8_dequantize_kernel");
+    return MOK_OK;
+}
+
 }  // namespace mok
 
 extern "C" int mok_mxfp8_quantize(const void* x_bf16, int num_matrices, int rows, int cols, void* x_fp8, void* x_sc,
@@ -85,10 +182,27 @@ extern "C" int mok_mxfp8_quantize(const void* x_bf16, int num_matrices, int rows
     if ((x_fp8 == nullptr) != (x_sc == nullptr) || (x_fp8_t == nullptr) != (x_sc_t == nullptr)) return MOK_ERR_INVALID_ARGUMENT;
     if (x_fp8 == nullptr && x_fp8_t == nullptr) return MOK_ERR_INVALID_ARGUMENT;
     if (num_matrices > 65535 || rows / 128 > 65535) return MOK_ERR_TOO_LARGE;
+    const long long elems = static_cast<long long>(rows) * cols;
+    QuantArgs a{};
+    a.x = static_cast<const bf16*>(x_bf16);
+    a.x_ld = cols;
+    a.x_mat_stride = elems;
+    a.q = static_cast<uint8_t*>(x_fp8);
+    a.q_mat_stride = elems;
+    a.sc = static_cast<uint8_t*>(x_sc);
+    a.sc_row_tile_stride = static_cast<long long>(cols / 128) * 512;
+    a.sc_mat_stride = static_cast<long long>(rows / 128) * a.sc_row_tile_stride;
+    a.qt = static_cast<uint8_t*>(x_fp8_t);
+    a.qt_ld = rows;
+    a.qt_mat_stride = elems;
+    a.sct = static_cast<uint8_t*>(x_sc_t);
+    a.sct_row_tile_stride = static_cast<long long>(rows / 128) * 512;
+    a.sct_mat_stride = static_cast<long long>(cols / 128) * a.sct_row_tile_stride;
+    a.num_tokens = nullptr;
+    a.row_begin = 0;
+    a.row_end = rows;
     dim3 grid(cols / 128, rows / 128, num_matrices);
-    quantize_kernel<<<grid, 128, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
-        static_cast<const bf16*>(x_bf16), rows, cols, static_cast<uint8_t*>(x_fp8), static_cast<uint8_t*>(x_sc),
-        static_cast<uint8_t*>(x_fp8_t), static_cast<uint8_t*>(x_sc_t));
+    quantize_kernel<<<grid, 128, 0, reinterpret_cast<cudaStream_t>(stream)>>>(a);
     MOK_LAUNCH_CHECK("mxfp8_quantize_kernel");
     return MOK_OK;
 }

@@ -40,7 +40,12 @@ class LayerArgs(ctypes.Structure):
             "d_x_shared", "d_x_routed", "d_gate_shared", "d_up_shared", "d_hidden_shared",
             "d_gate_routed", "d_up_routed", "d_hidden_routed", "d_y_routed",
             "d_w_shared_gate", "d_w_shared_up", "d_w_shared_down", "d_w_routed_gate", "d_w_routed_up", "d_w_routed_down",
-            "row_scratch", "status")]
+            "row_scratch", "status",
+            "w_gate_fp8", "w_gate_sc", "w_up_fp8", "w_up_sc", "w_down_fp8", "w_down_sc",
+            "w_gate_t_fp8", "w_gate_t_sc", "w_up_t_fp8", "w_up_t_sc", "w_down_t_fp8", "w_down_t_sc",
+            "x_fp8", "x_sc", "x_fp8_t", "x_sc_t", "gate_fp8", "gate_sc", "up_fp8", "up_sc",
+            "hidden_fp8", "hidden_sc", "hidden_fp8_t", "hidden_sc_t", "d_y_fp8", "d_y_sc", "d_y_fp8_t", "d_y_sc_t",
+            "d_gate_fp8", "d_gate_sc", "d_up_fp8", "d_up_sc", "d_gate_fp8_t", "d_gate_sc_t", "d_up_fp8_t", "d_up_sc_t")]
     )
 
 
@@ -66,8 +71,10 @@ def lib() -> ctypes.CDLL:
         L.mok_fwd_epilogue.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_void_p]
         L.mok_bwd_epilogue.argtypes = [c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_void_p]
         L.mok_mxfp8_quantize.argtypes = [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]
-        for name in ("mok_moe_forward_bf16", "mok_moe_recompute_bf16", "mok_moe_backward_bf16"):
+        for name in ("mok_moe_forward_bf16", "mok_moe_recompute_bf16", "mok_moe_backward_bf16",
+                     "mok_moe_forward_mxfp8", "mok_moe_recompute_mxfp8", "mok_moe_backward_mxfp8"):
             getattr(L, name).argtypes = [POINTER(LayerArgs), c_void_p]
+            getattr(L, name).restype = c_int
         L.mok_grouped_gemm_bf16.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
                                             c_int, c_void_p, c_void_p]
         L.mok_grouped_wgrad_bf16.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,

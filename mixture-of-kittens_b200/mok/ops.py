@@ -133,6 +133,32 @@ def _keep(args: LayerArgs, **arrays):
     return args
 
 
+def _set_ptrs(args: LayerArgs, **tensors) -> None:
+    for field, tensor in tensors.items():
+        setattr(args, field, None if tensor is None else tensor.data_ptr())
+
+
+def _new_fp8(like: torch.Tensor, rows: int, cols: int):
+    """An e4m3 [rows, cols] buffer and its e8m0 scale tiles [rows/128, cols/128, 32, 16]."""
+    return (like.new_empty((rows, cols), dtype=torch.float8_e4m3fn),
+            like.new_empty((rows // 128, cols // 128, 32, 16), dtype=torch.uint8))
+
+
+def _check_fp8_pair(name: str, data: torch.Tensor, scales: torch.Tensor, shape, device) -> None:
+    rows = 1
+    for s in shape[:-1]:
+        rows *= s
+    _require(tuple(data.shape) == tuple(shape), f"{name} must have shape {tuple(shape)}")
+    _require(tuple(scales.shape) == (rows // 128, shape[-1] // 128, 32, 16),
+             f"{name}_sc must have shape {(rows // 128, shape[-1] // 128, 32, 16)}")
+    _require(data.device == device and scales.device == device, f"{name} and its scales must be on {device}")
+    _require(data.dtype == torch.float8_e4m3fn and scales.dtype == torch.uint8 and data.is_contiguous() and scales.is_contiguous(),
+             f"{name} must be contiguous float8_e4m3fn with contiguous uint8 scales", TypeError)
+
+
+_check_fp8_weight = _check_fp8_pair
+
+
 # ------------------------------------------------------------------------------------------------------------
 # schedule-side ops
 # ------------------------------------------------------------------------------------------------------------
@@ -596,7 +622,47 @@ def dispatch_mlp_swiglu_combine_fwd_mxfp8(
     Outputs: x_fp8_t_routed [H,MB], x_sc_t_routed, gate_shared, gate_fp8_routed [MB,I], gate_sc_routed, up_shared,
              up_fp8_routed, up_sc_routed, hidden_shared, hidden_fp8_t_routed [I,MB], hidden_sc_t_routed, y_shared, y_routed
     """
-    raise NotImplementedError("the MXFP8 layer path is not available in this build")
+    T, H, I, E = _check_activation_dims(x, w_shared_gate, w_routed_gate)
+    _check_layer_scalars(topk, swiglu_limit, num_comm_sms, macrobatch_size, minibatch_size)
+    ep_size = _check_ptr_list("x_ptrs", x_ptrs)
+    _check_ptr_list("combine_buffer_ptrs", combine_buffer_ptrs, ep_size)
+    cap = _check_schedule(schedule_peer_rank)
+    MB = macrobatch_size
+    _check_shapes_devices(x.device, (
+        ("combine_buffer", combine_buffer, (T * topk, H)),
+        ("w_shared_gate", w_shared_gate, (I, H)), ("w_shared_up", w_shared_up, (I, H)), ("w_shared_down", w_shared_down, (H, I)),
+        ("schedule_peer_token_idx", schedule_peer_token_idx, (cap,)),
+        ("num_tokens", num_tokens, (1,)), ("tokens_per_expert", tokens_per_expert, (E,)),
+    ))
+    _check_fp8_weight("w_routed_gate", w_routed_gate, w_routed_gate_sc, (E, I, H), x.device)
+    _check_fp8_weight("w_routed_up", w_routed_up, w_routed_up_sc, (E, I, H), x.device)
+    _check_fp8_weight("w_routed_down", w_routed_down, w_routed_down_sc, (E, H, I), x.device)
+    _check_bf16_contiguous((("x", x), ("w_shared_gate", w_shared_gate), ("w_shared_up", w_shared_up),
+                            ("w_shared_down", w_shared_down)))
+
+    new = lambda *shape: x.new_empty(shape)  # noqa: E731
+    x_t, x_t_sc = _new_fp8(x, H, MB)
+    gate_q, gate_sc = _new_fp8(x, MB, I)
+    up_q, up_sc = _new_fp8(x, MB, I)
+    hid_t, hid_t_sc = _new_fp8(x, I, MB)
+    gate_shared, up_shared, hidden_shared, y_shared, y_routed = new(T, I), new(T, I), new(T, I), new(T, H), new(MB, H)
+    scratch = dict(x_routed=new(MB, H), gate_routed=new(MB, I), up_routed=new(MB, I), hidden_routed=new(MB, I))
+    x_q, x_sc = _new_fp8(x, MB, H)
+    hid_q, hid_sc = _new_fp8(x, MB, I)
+
+    a = _layer_args(ep_size=ep_size, rank=_local_rank(x, x_ptrs), x=x, intermediate=I, num_local_experts=E, topk=topk,
+                    capacity=cap, macrobatch_size=MB, minibatch_size=minibatch_size, num_comm_sms=num_comm_sms,
+                    swiglu_limit=swiglu_limit)
+    _keep(a, x_ptrs=x_ptrs, combine_ptrs=combine_buffer_ptrs)
+    _set_ptrs(a, peer_rank=schedule_peer_rank, peer_token_idx=schedule_peer_token_idx, num_tokens=num_tokens,
+              tokens_per_expert=tokens_per_expert, w_shared_gate=w_shared_gate, w_shared_up=w_shared_up,
+              w_shared_down=w_shared_down, w_gate_fp8=w_routed_gate, w_gate_sc=w_routed_gate_sc, w_up_fp8=w_routed_up,
+              w_up_sc=w_routed_up_sc, w_down_fp8=w_routed_down, w_down_sc=w_routed_down_sc,
+              gate_shared=gate_shared, up_shared=up_shared, hidden_shared=hidden_shared, y_shared=y_shared, y_routed=y_routed,
+              x_fp8=x_q, x_sc=x_sc, x_fp8_t=x_t, x_sc_t=x_t_sc, gate_fp8=gate_q, gate_sc=gate_sc, up_fp8=up_q, up_sc=up_sc,
+              hidden_fp8=hid_q, hidden_sc=hid_sc, hidden_fp8_t=hid_t, hidden_sc_t=hid_t_sc, **scratch)
+    check(lib().mok_moe_forward_mxfp8(_native.ctypes.byref(a), stream_ptr(x.device)), "dispatch_mlp_swiglu_combine_fwd_mxfp8")
+    return (x_t, x_t_sc, gate_shared, gate_q, gate_sc, up_shared, up_q, up_sc, hidden_shared, hid_t, hid_t_sc, y_shared, y_routed)
 
 
 @torch.library.custom_op("mok::recompute_forward_context_mxfp8", mutates_args=())
@@ -620,8 +686,46 @@ def recompute_forward_context_mxfp8(
     minibatch_size: int,
 ) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor,
            torch.Tensor, torch.Tensor, torch.Tensor]:
-    """MXFP8 context recomputation (first macrobatch)."""
-    raise NotImplementedError("the MXFP8 layer path is not available in this build")
+    """MXFP8 context recomputation (first macrobatch): dispatch, quantize, gate / up GEMMs, SwiGLU, quantize.
+
+    Outputs: x_fp8_t_routed, x_sc_t_routed, gate_shared, gate_fp8_routed, gate_sc_routed, up_shared, up_fp8_routed,
+             up_sc_routed, hidden_shared, hidden_fp8_t_routed, hidden_sc_t_routed
+    """
+    T, H, I, E = _check_activation_dims(x, w_shared_gate, w_routed_gate)
+    _check_layer_scalars(topk, swiglu_limit, num_comm_sms, macrobatch_size, minibatch_size)
+    ep_size = _check_ptr_list("x_ptrs", x_ptrs)
+    cap = _check_schedule(schedule_peer_rank)
+    MB = macrobatch_size
+    _check_shapes_devices(x.device, (
+        ("w_shared_gate", w_shared_gate, (I, H)), ("w_shared_up", w_shared_up, (I, H)),
+        ("schedule_peer_token_idx", schedule_peer_token_idx, (cap,)),
+        ("num_tokens", num_tokens, (1,)), ("tokens_per_expert", tokens_per_expert, (E,)),
+    ))
+    _check_fp8_weight("w_routed_gate", w_routed_gate, w_routed_gate_sc, (E, I, H), x.device)
+    _check_fp8_weight("w_routed_up", w_routed_up, w_routed_up_sc, (E, I, H), x.device)
+    _check_bf16_contiguous((("x", x), ("w_shared_gate", w_shared_gate), ("w_shared_up", w_shared_up)))
+
+    new = lambda *shape: x.new_empty(shape)  # noqa: E731
+    x_t, x_t_sc = _new_fp8(x, H, MB)
+    gate_q, gate_sc = _new_fp8(x, MB, I)
+    up_q, up_sc = _new_fp8(x, MB, I)
+    hid_t, hid_t_sc = _new_fp8(x, I, MB)
+    gate_shared, up_shared, hidden_shared = new(T, I), new(T, I), new(T, I)
+    scratch = dict(x_routed=new(MB, H), gate_routed=new(MB, I), up_routed=new(MB, I), hidden_routed=new(MB, I))
+    x_q, x_sc = _new_fp8(x, MB, H)
+    hid_q, hid_sc = _new_fp8(x, MB, I)
+    a = _layer_args(ep_size=ep_size, rank=_local_rank(x, x_ptrs), x=x, intermediate=I, num_local_experts=E, topk=topk,
+                    capacity=cap, macrobatch_size=MB, minibatch_size=minibatch_size, num_comm_sms=num_comm_sms,
+                    swiglu_limit=swiglu_limit)
+    _keep(a, x_ptrs=x_ptrs)
+    _set_ptrs(a, peer_rank=schedule_peer_rank, peer_token_idx=schedule_peer_token_idx, num_tokens=num_tokens,
+              tokens_per_expert=tokens_per_expert, w_shared_gate=w_shared_gate, w_shared_up=w_shared_up,
+              w_gate_fp8=w_routed_gate, w_gate_sc=w_routed_gate_sc, w_up_fp8=w_routed_up, w_up_sc=w_routed_up_sc,
+              gate_shared=gate_shared, up_shared=up_shared, hidden_shared=hidden_shared,
+              x_fp8=x_q, x_sc=x_sc, x_fp8_t=x_t, x_sc_t=x_t_sc, gate_fp8=gate_q, gate_sc=gate_sc, up_fp8=up_q, up_sc=up_sc,
+              hidden_fp8=hid_q, hidden_sc=hid_sc, hidden_fp8_t=hid_t, hidden_sc_t=hid_t_sc, **scratch)
+    check(lib().mok_moe_recompute_mxfp8(_native.ctypes.byref(a), stream_ptr(x.device)), "recompute_forward_context_mxfp8")
+    return (x_t, x_t_sc, gate_shared, gate_q, gate_sc, up_shared, up_q, up_sc, hidden_shared, hid_t, hid_t_sc)
 
 
 @torch.library.custom_op(
@@ -676,5 +780,84 @@ def dispatch_mlp_swiglu_combine_bwd_mxfp8(
 ) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor,
            torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor,
            torch.Tensor, torch.Tensor]:
-    """MXFP8 backward of the layer."""
-    raise NotImplementedError("the MXFP8 layer path is not available in this build")
+    """MXFP8 backward of the layer.
+
+    Outputs: d_x_shared [T,H], d_x_routed [MB,H], d_gate_shared, d_gate_fp8_routed [MB,I], d_gate_sc_routed, d_up_shared,
+             d_up_fp8_routed, d_up_sc_routed, d_hidden_shared, d_hidden_routed [MB,I] bf16, d_y_fp8_routed [MB,H],
+             d_y_sc_routed, d_w_shared_gate, d_w_routed_gate, d_w_shared_up, d_w_routed_up, d_w_shared_down, d_w_routed_down
+    """
+    T, H, I, E = _check_activation_dims(x, w_shared_gate, w_routed_gate)
+    _check_layer_scalars(topk, swiglu_limit, num_comm_sms, macrobatch_size, minibatch_size)
+    ep_size = _check_ptr_list("x_ptrs", x_ptrs)
+    for name, pointers in (("d_y_buffer_ptrs", d_y_buffer_ptrs), ("d_x_routed_buffer_ptrs", d_x_routed_buffer_ptrs),
+                           ("router_weight_buffer_ptrs", router_weight_buffer_ptrs),
+                           ("d_router_weight_buffer_ptrs", d_router_weight_buffer_ptrs)):
+        _check_ptr_list(name, pointers, ep_size)
+    cap = _check_schedule(schedule_peer_rank)
+    MB = macrobatch_size
+    dev = x.device
+    _check_shapes_devices(dev, (
+        ("d_y_buffer", d_y_buffer, (T, H)), ("d_x_routed_buffer", d_x_routed_buffer, (T * topk, H)),
+        ("router_weight_buffer", router_weight_buffer, (T, topk)), ("d_router_weight_buffer", d_router_weight_buffer, (T, topk)),
+        ("w_shared_gate", w_shared_gate, (I, H)), ("w_shared_up", w_shared_up, (I, H)), ("w_shared_down", w_shared_down, (H, I)),
+        ("gate_shared", gate_shared, (T, I)), ("up_shared", up_shared, (T, I)), ("hidden_shared", hidden_shared, (T, I)),
+        ("schedule_peer_token_idx", schedule_peer_token_idx, (cap,)),
+        ("num_tokens", num_tokens, (1,)), ("tokens_per_expert", tokens_per_expert, (E,)),
+    ))
+    _check_fp8_weight("w_routed_gate", w_routed_gate, w_routed_gate_sc, (E, I, H), dev)
+    _check_fp8_weight("w_routed_up", w_routed_up, w_routed_up_sc, (E, I, H), dev)
+    _check_fp8_weight("w_routed_gate_T", w_routed_gate_T, w_routed_gate_T_sc, (E, H, I), dev)
+    _check_fp8_weight("w_routed_up_T", w_routed_up_T, w_routed_up_T_sc, (E, H, I), dev)
+    _check_fp8_weight("w_routed_down_T", w_routed_down_T, w_routed_down_T_sc, (E, I, H), dev)
+    _check_fp8_pair("x_fp8_t_routed", x_fp8_t_routed, x_sc_t_routed, (H, MB), dev)
+    _check_fp8_pair("gate_fp8_routed", gate_fp8_routed, gate_sc_routed, (MB, I), dev)
+    _check_fp8_pair("up_fp8_routed", up_fp8_routed, up_sc_routed, (MB, I), dev)
+    _check_fp8_pair("hidden_fp8_t_routed", hidden_fp8_t_routed, hidden_sc_t_routed, (I, MB), dev)
+    _check_bf16_contiguous((("x", x), ("d_y_buffer", d_y_buffer), ("gate_shared", gate_shared), ("up_shared", up_shared),
+                            ("hidden_shared", hidden_shared), ("w_shared_gate", w_shared_gate), ("w_shared_up", w_shared_up),
+                            ("w_shared_down", w_shared_down)))
+
+    new = lambda *shape: x.new_empty(shape)  # noqa: E731
+    d_x_shared, d_x_routed, d_hidden_routed = new(T, H), new(MB, H), new(MB, I)
+    d_gate_shared, d_up_shared, d_hidden_shared = new(T, I), new(T, I), new(T, I)
+    d_gate_q, d_gate_sc = _new_fp8(x, MB, I)
+    d_up_q, d_up_sc = _new_fp8(x, MB, I)
+    d_y_q, d_y_sc = _new_fp8(x, MB, H)
+    d_w_shared_gate, d_w_shared_up, d_w_shared_down = new(I, H), new(I, H), new(H, I)
+    d_w_routed_gate, d_w_routed_up, d_w_routed_down = new(E, I, H), new(E, I, H), new(E, H, I)
+    scratch = dict(x_routed=new(MB, H), gate_routed=new(MB, I), up_routed=new(MB, I), hidden_routed=new(MB, I),
+                   d_y_routed=new(MB, H), d_gate_routed=new(MB, I), d_up_routed=new(MB, I))
+    x_q, x_sc = _new_fp8(x, MB, H)
+    hid_q, hid_sc = _new_fp8(x, MB, I)
+    d_y_t, d_y_t_sc = _new_fp8(x, H, MB)
+    d_gate_t, d_gate_t_sc = _new_fp8(x, I, MB)
+    d_up_t, d_up_t_sc = _new_fp8(x, I, MB)
+    row_scratch = torch.empty(2 * MB, dtype=torch.float32, device=dev)
+
+    a = _layer_args(ep_size=ep_size, rank=_local_rank(x, x_ptrs), x=x, intermediate=I, num_local_experts=E, topk=topk,
+                    capacity=cap, macrobatch_size=MB, minibatch_size=minibatch_size, num_comm_sms=num_comm_sms,
+                    swiglu_limit=swiglu_limit)
+    _keep(a, x_ptrs=x_ptrs, d_y_ptrs=d_y_buffer_ptrs, d_x_routed_ptrs=d_x_routed_buffer_ptrs,
+          router_weight_ptrs=router_weight_buffer_ptrs, d_router_weight_ptrs=d_router_weight_buffer_ptrs)
+    _set_ptrs(a, peer_rank=schedule_peer_rank, peer_token_idx=schedule_peer_token_idx, num_tokens=num_tokens,
+              tokens_per_expert=tokens_per_expert, d_y_local=d_y_buffer,
+              w_shared_gate=w_shared_gate, w_shared_up=w_shared_up, w_shared_down=w_shared_down,
+              w_gate_fp8=w_routed_gate, w_gate_sc=w_routed_gate_sc, w_up_fp8=w_routed_up, w_up_sc=w_routed_up_sc,
+              w_gate_t_fp8=w_routed_gate_T, w_gate_t_sc=w_routed_gate_T_sc, w_up_t_fp8=w_routed_up_T, w_up_t_sc=w_routed_up_T_sc,
+              w_down_t_fp8=w_routed_down_T, w_down_t_sc=w_routed_down_T_sc,
+              gate_shared=gate_shared, up_shared=up_shared, hidden_shared=hidden_shared,
+              x_fp8=x_q, x_sc=x_sc, x_fp8_t=x_fp8_t_routed, x_sc_t=x_sc_t_routed, gate_fp8=gate_fp8_routed, gate_sc=gate_sc_routed,
+              up_fp8=up_fp8_routed, up_sc=up_sc_routed, hidden_fp8=hid_q, hidden_sc=hid_sc,
+              hidden_fp8_t=hidden_fp8_t_routed, hidden_sc_t=hidden_sc_t_routed,
+              d_x_shared=d_x_shared, d_x_routed=d_x_routed, d_hidden_routed=d_hidden_routed,
+              d_gate_shared=d_gate_shared, d_up_shared=d_up_shared, d_hidden_shared=d_hidden_shared,
+              d_y_fp8=d_y_q, d_y_sc=d_y_sc, d_y_fp8_t=d_y_t, d_y_sc_t=d_y_t_sc,
+              d_gate_fp8=d_gate_q, d_gate_sc=d_gate_sc, d_up_fp8=d_up_q, d_up_sc=d_up_sc,
+              d_gate_fp8_t=d_gate_t, d_gate_sc_t=d_gate_t_sc, d_up_fp8_t=d_up_t, d_up_sc_t=d_up_t_sc,
+              d_w_shared_gate=d_w_shared_gate, d_w_shared_up=d_w_shared_up, d_w_shared_down=d_w_shared_down,
+              d_w_routed_gate=d_w_routed_gate, d_w_routed_up=d_w_routed_up, d_w_routed_down=d_w_routed_down,
+              row_scratch=row_scratch, **scratch)
+    check(lib().mok_moe_backward_mxfp8(_native.ctypes.byref(a), stream_ptr(dev)), "dispatch_mlp_swiglu_combine_bwd_mxfp8")
+    return (d_x_shared, d_x_routed, d_gate_shared, d_gate_q, d_gate_sc, d_up_shared, d_up_q, d_up_sc, d_hidden_shared,
+            d_hidden_routed, d_y_q, d_y_sc, d_w_shared_gate, d_w_routed_gate, d_w_shared_up, d_w_routed_up, d_w_shared_down,
+            d_w_routed_down)

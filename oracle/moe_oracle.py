@@ -259,8 +259,43 @@ def _ffn_bwd(x, gate, up, hidden, d_y, wg, wu, wd, limit, rnd):
     return d_x, d_wg, d_wu, d_wd, d_hidden, hidden_f
 
 
+def _qdq(t: torch.Tensor) -> torch.Tensor:
+    """Value after an MXFP8 round trip with blocks of 32 along the last dimension (dims padded to 128 with zeros,
+    which changes no block that holds data)."""
+    r, c = t.shape
+    rp, cp = -(-r // 128) * 128, -(-c // 128) * 128
+    buf = torch.zeros(rp, cp, dtype=torch.bfloat16)
+    buf[:r, :c] = t.to(torch.bfloat16)
+    q, sc = mxfp8_quantize_rows_oracle(buf)
+    return mxfp8_dequantize_oracle(q, sc)[:r, :c]
+
+
+def _ffn_mxfp8(x, d_y, wg, wu, wd, limit):
+    """Routed expert forward + backward with MXFP8 operands, quantized where the device path quantizes
+    (csrc/megakernel/forward.cuh / backward.cuh of the reference: x after dispatch, gate / up after their GEMM,
+    hidden after SwiGLU, d_y*w after dispatch, d_gate / d_up after SwiGLU backward; weights and their transposes are
+    quantized separately; wgrad operands are quantized along the schedule rows).  Rows of x / d_y are in schedule order."""
+    wg_q, wu_q, wd_q = _qdq(wg), _qdq(wu), _qdq(wd)                   # [I,H] [I,H] [H,I], blocks along K of the forward GEMMs
+    wg_t, wu_t, wd_t = _qdq(wg.T.contiguous()), _qdq(wu.T.contiguous()), _qdq(wd.T.contiguous())   # [H,I] [H,I] [I,H]
+    x_q = _qdq(x)
+    gate, up = _bf16(x_q @ wg_q.T), _bf16(x_q @ wu_q.T)
+    hidden = _bf16(swiglu_oracle(gate, up, limit))
+    y = _bf16(_qdq(hidden) @ wd_q.T)
+    gate_s, up_s = _qdq(gate), _qdq(up)                              # what backward reads back
+    d_hidden = _bf16(_qdq(d_y) @ wd_t.T)
+    d_gate, d_up, hidden_f = swiglu_bwd_oracle(gate_s, up_s, d_hidden, limit)
+    d_gate, d_up = _bf16(d_gate), _bf16(d_up)
+    d_x = _bf16(_qdq(d_gate) @ wg_t.T + _qdq(d_up) @ wu_t.T)
+    x_t, hid_t = _qdq(x.T.contiguous()), _qdq(hidden.T.contiguous())  # blocks of 32 along the schedule rows
+    d_wd = _qdq(d_y.T.contiguous()) @ hid_t.T
+    d_wg = _qdq(d_gate.T.contiguous()) @ x_t.T
+    d_wu = _qdq(d_up.T.contiguous()) @ x_t.T
+    d_router = (d_hidden * hidden_f).sum(-1)                          # still to be divided by the router weight
+    return y, d_x, d_wg, d_wu, d_wd, d_router
+
+
 def moe_layer_oracle(ranks: list[RankInputs], swiglu_limit: float | None = None,
-                     round_bf16: bool = True) -> list[RankOutputs]:
+                     round_bf16: bool = True, mxfp8: bool = False) -> list[RankOutputs]:
     """Forward + backward of the EP MoE layer for every rank (tests/utils.py:320-432).
 
     round_bf16=True rounds to bf16 at the points where the CUDA path stores bf16 (gate, up,
@@ -282,7 +317,33 @@ def moe_layer_oracle(ranks: list[RankInputs], swiglu_limit: float | None = None,
     d_wu = [torch.zeros_like(d_wg[0]) for _ in range(ep)]
     d_wd = [torch.zeros(e_loc, *ranks[0].w_routed_down.shape[1:]) for _ in range(ep)]
 
-    for owner in range(ep):
+    if mxfp8:
+        topk_all = np.stack([r.topk_experts.to(torch.int32).numpy() for r in ranks])
+        cap = (t_loc * k * ep // 256 + e_loc + 1) * 256
+    for owner in range(ep if mxfp8 else 0):
+        pr, pt, _, tpe = schedule_oracle(topk_all, e_loc, cap, owner)
+        base = 0
+        for e in range(e_loc):
+            rows = np.arange(base, base + int(tpe[e]))
+            rows = rows[pr[rows] >= 0]                                  # schedule order, padding dropped
+            base += int(tpe[e])
+            src = torch.from_numpy(pr[rows].astype(np.int64))
+            route = torch.from_numpy(pt[rows].astype(np.int64))
+            if rows.size == 0:
+                continue
+            xe = torch.stack([ranks[int(s)].x.float()[int(r) // k] for s, r in zip(src, route)])
+            w = torch.stack([ranks[int(s)].router_weights.reshape(-1)[int(r)].float() for s, r in zip(src, route)])
+            dye = _bf16(torch.stack([ranks[int(s)].d_output.float()[int(r) // k] for s, r in zip(src, route)]) * w[:, None])
+            y, dxe, g_wg, g_wu, g_wd, d_router = _ffn_mxfp8(xe, dye, ranks[owner].w_routed_gate[e], ranks[owner].w_routed_up[e],
+                                                            ranks[owner].w_routed_down[e], swiglu_limit)
+            d_wg[owner][e], d_wu[owner][e], d_wd[owner][e] = g_wg, g_wu, g_wd
+            for s in range(ep):
+                m = src == s
+                combine[s][route[m]] = y[m]
+                d_x_routed[s][route[m]] = dxe[m]
+                d_rw[s][route[m]] = torch.where(w[m] > 0, d_router[m] / w[m], torch.zeros_like(w[m]))
+
+    for owner in range(0 if mxfp8 else ep):
         for e in range(e_loc):
             ge = owner * e_loc + e
             xs, dys, where = [], [], []
@@ -320,7 +381,7 @@ def moe_layer_oracle(ranks: list[RankInputs], swiglu_limit: float | None = None,
         for i in range(k):
             acc += w[:, i:i + 1] * routed[:, i]
             dacc += dxr[:, i]
-        d_router = (d_out[:, None, :] * routed).sum(-1)
+        d_router = d_rw[r].view(t_loc, k) if mxfp8 else (d_out[:, None, :] * routed).sum(-1)
         results.append(RankOutputs(
             output=acc.to(out_dtype), d_x=dacc.to(out_dtype), d_router_weights=d_router,
             d_w_routed_gate=d_wg[r].to(out_dtype), d_w_routed_up=d_wu[r].to(out_dtype),

@@ -64,6 +64,88 @@ def test_mxfp8_grouped_gemm(dev, counts, N, K):
     assert _rel_l2(plain, got) <= 6e-2, f"vs unquantized operands: {_rel_l2(plain, got):.3e}"
 
 
+FIELDS = ("d_x", "d_router_weights", "d_w_routed_gate", "d_w_routed_up", "d_w_routed_down",
+          "d_w_shared_gate", "d_w_shared_up", "d_w_shared_down")
+
+
+def _run_mxfp8_layer(dist_ctx, inp, E, config, limit=None, recompute=False):
+    import torch.distributed as dist
+    import mok
+    F = mok.functional
+    _, _, dev = dist_ctx
+    d = {k: (v.to(dev) if torch.is_tensor(v) else v) for k, v in vars(inp).items()}
+    T, H = inp.x.shape
+    K = inp.topk_experts.shape[1]
+    ws = F.get_workspace(config, dist.group.WORLD, device=dev, num_local_tokens=T, hidden_size=H, topk=K)
+    sched = F.build_schedule(ws, config, d["topk_experts"], num_local_experts=E)
+    g = mok.ops.mxfp8_quantize(d["w_routed_gate"], True, True)
+    u = mok.ops.mxfp8_quantize(d["w_routed_up"], True, True)
+    dn = mok.ops.mxfp8_quantize(d["w_routed_down"], True, True)
+    shared = (d["w_shared_gate"], d["w_shared_up"], d["w_shared_down"])
+    out, ctx = F.forward(config, ws, sched, d["x"], d["router_weights"], *shared, (g[0], g[1]), (u[0], u[1]), (dn[0], dn[1]),
+                         swiglu_limit=limit)
+    if recompute:
+        ctx2 = F.recompute_forward_context(config, ws, sched, d["x"], shared[0], shared[1], (g[0], g[1]), (u[0], u[1]),
+                                           swiglu_limit=limit)
+        n = min(int(sched.num_tokens.item()), config.macrobatch_size)
+        for name in ("gate_routed", "up_routed"):           # [MB, I] data, scale tiles by row tile
+            for a, b in zip(getattr(ctx, name), getattr(ctx2, name)):
+                rows = n if a.dtype == torch.float8_e4m3fn else n // 128
+                assert torch.equal(a[:rows].view(torch.uint8), b[:rows].view(torch.uint8)), name
+        for name in ("x_routed", "hidden_routed"):          # transposed [cols, MB]
+            a, b = getattr(ctx, name)[0], getattr(ctx2, name)[0]
+            assert torch.equal(a[:, :n].view(torch.uint8), b[:, :n].view(torch.uint8)), name
+        ctx = ctx2
+    grads = F.backward(config, ws, sched, ctx, d["d_output"], d["x"], d["router_weights"], *shared, g, u, (dn[2], dn[3]),
+                       swiglu_limit=limit)
+    torch.cuda.synchronize()
+    mok.ops.check_status(dev)
+    return out, grads
+
+
+MX_CASES = [
+    ("small", 4, 256, 512, 2, 512, {}, None, False),
+    # limit 4.0 as in the reference tests: a tighter clamp puts many gate values next to the threshold, where the
+    # e4m3 rounding of the saved gate flips the gradient mask and the comparison with BF16 math stops being meaningful
+    ("clamped-recompute", 4, 512, 256, 2, 512, {}, 4.0, True),
+    ("ring-2-windows", 4, 256, 256, 4, 512, dict(minibatch_size=256, macrobatch_size=2048), None, False),
+    ("many-experts", 32, 256, 256, 8, 1024, {}, None, False),
+]
+
+
+@pytest.mark.parametrize("case", MX_CASES, ids=[c[0] for c in MX_CASES])
+def test_mxfp8_layer_fwd_bwd(dist_ctx, case):
+    """Whole layer in MXFP8 against (1) a CPU oracle that quantizes at the same points: rel-L2 <= 3e-2, and (2) the plain
+    BF16 oracle inside the reference's MXFP8 tolerance: max |diff| <= 1.0, sum|diff|/sum|ref| <= 0.1, cosine >= 0.996."""
+    import mok
+    name, E, H, I, K, T, cfg, limit, recompute = case
+    config = mok.functional.MoKConfig(**cfg)
+    inp = O.make_rank_inputs(0, E, E, K, T, H, I)
+    emu = O.moe_layer_oracle([inp], swiglu_limit=limit, mxfp8=True)[0]
+    ref = O.moe_layer_oracle([inp], swiglu_limit=limit)[0]
+    out, grads = _run_mxfp8_layer(dist_ctx, inp, E, config, limit, recompute)
+    problems = []
+    for field, got in (("output", out),) + tuple(zip(FIELDS, grads)):
+        g = got.float().cpu()
+        _, _, l2, _ = O.error_stats(getattr(emu, field).float(), g)
+        mx, l1, _, cos = O.error_stats(getattr(ref, field).float(), g)
+        if not (l2 <= 3e-2 and mx <= 1.0 and l1 <= 0.1 and cos >= 0.996):
+            problems.append(f"{field}: vs-emulation l2 {l2:.3e}; vs-bf16 max {mx:.3e} l1 {l1:.3e} cos {cos:.5f}")
+    assert not problems, name + " | " + " ; ".join(problems)
+
+
+def test_mxfp8_layer_bitwise_repeat(dist_ctx):
+    import mok
+    E, H, I, K, T = 8, 256, 256, 2, 1024
+    config = mok.functional.MoKConfig(minibatch_size=256, macrobatch_size=1024)
+    inp = O.make_rank_inputs(0, E, E, K, T, H, I)
+    out1, grads1 = _run_mxfp8_layer(dist_ctx, inp, E, config)
+    out2, grads2 = _run_mxfp8_layer(dist_ctx, inp, E, config)
+    assert torch.equal(out1, out2)
+    for name, a, b in zip(FIELDS, grads1, grads2):
+        assert torch.equal(a, b), f"{name} is not bitwise reproducible"
+
+
 @pytest.mark.parametrize("counts,M,N", [(None, 256, 256), ([256, 0, 768], 256, 512), ([512, 512], 512, 256)])
 def test_mxfp8_grouped_wgrad(dev, counts, M, N):
     from mok import _native as nat
