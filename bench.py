@@ -208,6 +208,52 @@ def time_gemm_forms(dev, w, e_loc, sched, weights, rows_buf):
     return out, rows_done
 
 
+def time_gemm_forms_mxfp8(dev, w, e_loc, sched, qg, qd, rows_buf):
+    """Single launches of the block-scaled MXFP8 GEMM on the layer's shapes (forward gate form, wgrad gate form)."""
+    import torch
+    import mok
+    from mok import _native as nat
+    H, I = w["H"], w["I"]
+    valid_rows = int((sched.peer_rank >= 0).sum().item())
+    padded_rows = int(sched.num_tokens.item())
+    rows_buf = min(rows_buf, (padded_rows + 255) // 256 * 256)
+    a = torch.randn(rows_buf, H, device=dev, dtype=torch.bfloat16)
+    a_q, a_sc, a_t, a_t_sc = mok.ops.mxfp8_quantize(a, True, True)
+    g = torch.randn(rows_buf, I, device=dev, dtype=torch.bfloat16)
+    _, _, g_t, g_t_sc = mok.ops.mxfp8_quantize(g, False, True)
+    del a, g
+    d_i = torch.empty(rows_buf, I, device=dev, dtype=torch.bfloat16)
+    d_w = torch.empty(e_loc, I, H, device=dev, dtype=torch.bfloat16)
+    st = nat.status_word(dev)
+    L = nat.lib()
+    tpe, nt = nat.ptr(sched.tokens_per_expert), nat.ptr(sched.num_tokens)
+
+    def fwd():
+        return L.mok_grouped_gemm_mxfp8(nat.ptr(a_q), nat.ptr(a_sc), nat.ptr(qg[0]), nat.ptr(qg[1]), nat.ptr(d_i), tpe, nt, e_loc,
+                                        rows_buf, I, H, nat.ptr(st), nat.stream_ptr(dev))
+
+    def wgrad():
+        return L.mok_grouped_wgrad_mxfp8(nat.ptr(g_t), nat.ptr(g_t_sc), nat.ptr(a_t), nat.ptr(a_t_sc), nat.ptr(d_w), tpe, nt, e_loc,
+                                         rows_buf, I, H, nat.ptr(st), nat.stream_ptr(dev))
+    out = {}
+    rows_done = min(valid_rows, rows_buf)
+    for name, fn in (("fwd_gate", fwd), ("wgrad_gate", wgrad)):
+        for _ in range(2):
+            nat.check(fn(), name)
+        ev = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
+        reps = 5
+        torch.cuda.synchronize()
+        ev[0].record()
+        for _ in range(reps):
+            fn()
+        ev[1].record()
+        torch.cuda.synchronize()
+        ms = ev[0].elapsed_time(ev[1]) / reps
+        out[name] = {"ms": ms, "tflops": 2.0 * rows_done * H * I / (ms * 1e-3) / 1e12}
+    nat.check_status(dev)
+    return out, rows_done
+
+
 def run_gpu_arm(args, w):
     import torch
     import torch.distributed as dist
@@ -238,10 +284,22 @@ def run_gpu_arm(args, w):
     x, dy, topk, rw, weights = make_gpu_inputs(w, e_loc, rank, dev)
     ws = F.get_workspace(config, dist.group.WORLD, device=dev, num_local_tokens=T, hidden_size=H, topk=K)
 
+    mxfp8 = args.dtype == "mxfp8"
+    if mxfp8:   # routed weights are quantized once, outside the timed region, as a trainer caches them
+        qg = mok.ops.mxfp8_quantize(weights[3], True, True)
+        qu = mok.ops.mxfp8_quantize(weights[4], True, True)
+        qd = mok.ops.mxfp8_quantize(weights[5], True, True)
+        fwd_w = weights[:3] + ((qg[0], qg[1]), (qu[0], qu[1]), (qd[0], qd[1]))
+        bwd_w = weights[:3] + (qg, qu, (qd[2], qd[3]))
+        weights = weights[:3] + (None, None, None)       # the bf16 copies are not needed any more
+        torch.cuda.empty_cache()
+    else:
+        fwd_w = bwd_w = weights
+
     def step(x_, dy_, topk_, rw_):
         sched = F.build_schedule(ws, config, topk_, num_local_experts=e_loc)
-        out, ctx = F.forward(config, ws, sched, x_, rw_, *weights)
-        grads = F.backward(config, ws, sched, ctx, dy_, x_, rw_, *weights)
+        out, ctx = F.forward(config, ws, sched, x_, rw_, *fwd_w)
+        grads = F.backward(config, ws, sched, ctx, dy_, x_, rw_, *bwd_w)
         return sched, out, grads
 
     def timed(fn, steps):
@@ -289,24 +347,35 @@ def run_gpu_arm(args, w):
 
     sched, out, grads = step(x, dy, topk, rw)
     del out, grads
-    forms, rows_done = time_gemm_forms(dev, w, e_loc, sched, weights, mb)
+    if mxfp8:
+        forms, rows_done = time_gemm_forms_mxfp8(dev, w, e_loc, sched, qg, qd, mb)
+    else:
+        forms, rows_done = time_gemm_forms(dev, w, e_loc, sched, weights, mb)
     if rank == 0:
         peaks = measured_peaks()
         tokens = T * world
         fl = flops_per_token(w) * T            # per rank
         dominant = forms["fwd_gate"]
+        # MXFP8: no measured fp8 figure exists on this pool; the dense fp8 rate of the part is twice its bf16 rate
+        peak_tc = peaks["burst"] * (2.0 if mxfp8 else 1.0)
+        peak_src = ("2 x " if mxfp8 else "") + peaks["source"] + " bf16 burst"
+        # DRAM bytes of one forward-form launch: ncu measured 56.3 KB per schedule row on a 16384-row capture with
+        # 1024 rows per expert (profiles/); scaled by rows, valid while the rows per expert stay near that
+        rows_per_expert = rows_done / max(1, e_loc)
+        traffic = int(56.3e3 * rows_done) if (not mxfp8 and 512 <= rows_per_expert <= 2048) else None
         line = {
             "metric": "moe_layer_fwd_bwd_tokens_per_s", "value": tokens / (ms_step * 1e-3), "unit": "tokens/s",
             "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step,
-            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": w["label"], "tokens_per_rank": T, "hidden": H, "experts": E, "intermediate": I, "topk": K,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": args.dtype, "data": "synthetic",
+            "config": {"workload": w["label"].replace("bf16", args.dtype), "tokens_per_rank": T, "hidden": H, "experts": E, "intermediate": I, "topk": K,
                        "shared_expert": True, "parallelism": f"ep{world}", "macrobatch_size": mb,
                        "schedule_capacity": capacity, "l2_policy": "inputs_larger_than_L2"},
             "tflops_per_gpu": fl / (ms_step * 1e-3) / 1e12,
             "frac_of_bf16_peak_sustained": fl / (ms_step * 1e-3) / 1e12 / peaks["sustained"],
-            "roofline": {"bound": "tensor", "kernel": "grouped_gemm_kernel (forward gate form)", "achieved": dominant["tflops"],
-                         "peak": peaks["burst"], "unit": "TFLOP/s", "frac": dominant["tflops"] / peaks["burst"],
-                         "traffic": None, "peak_source": peaks["source"], "rows": rows_done, "forms": forms},
+            "roofline": {"bound": "tensor",
+                         "kernel": ("mxfp8_gemm_kernel" if mxfp8 else "grouped_gemm_kernel") + " (forward gate form)",
+                         "achieved": dominant["tflops"], "peak": peak_tc, "unit": "TFLOP/s", "frac": dominant["tflops"] / peak_tc,
+                         "traffic": traffic, "peak_source": peak_src, "rows": rows_done, "forms": forms},
             "e2e": {"value": tokens / (ms_e2e * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
             "gpu_launches": int(launches), "clocks": clocks,
         }
@@ -356,6 +425,7 @@ def main():
     ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
     ap.add_argument("--macrobatch", type=int, default=0)
     ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--dtype", default="bf16", choices=("bf16", "mxfp8"))
     args = ap.parse_args()
     w = WORKLOADS[args.workload]
     if args.gemm_only:
