@@ -320,6 +320,9 @@ def moe_layer_oracle(ranks: list[RankInputs], swiglu_limit: float | None = None,
     if mxfp8:
         topk_all = np.stack([r.topk_experts.to(torch.int32).numpy() for r in ranks])
         cap = (t_loc * k * ep // 256 + e_loc + 1) * 256
+        x_all = torch.stack([r.x.float() for r in ranks])
+        dy_all = torch.stack([r.d_output.float() for r in ranks])
+        w_all = torch.stack([r.router_weights.reshape(-1).float() for r in ranks])
     for owner in range(ep if mxfp8 else 0):
         pr, pt, _, tpe = schedule_oracle(topk_all, e_loc, cap, owner)
         base = 0
@@ -331,9 +334,9 @@ def moe_layer_oracle(ranks: list[RankInputs], swiglu_limit: float | None = None,
             route = torch.from_numpy(pt[rows].astype(np.int64))
             if rows.size == 0:
                 continue
-            xe = torch.stack([ranks[int(s)].x.float()[int(r) // k] for s, r in zip(src, route)])
-            w = torch.stack([ranks[int(s)].router_weights.reshape(-1)[int(r)].float() for s, r in zip(src, route)])
-            dye = _bf16(torch.stack([ranks[int(s)].d_output.float()[int(r) // k] for s, r in zip(src, route)]) * w[:, None])
+            xe = x_all[src, route // k]
+            w = w_all[src, route]
+            dye = _bf16(dy_all[src, route // k] * w[:, None])
             y, dxe, g_wg, g_wu, g_wd, d_router = _ffn_mxfp8(xe, dye, ranks[owner].w_routed_gate[e], ranks[owner].w_routed_up[e],
                                                             ranks[owner].w_routed_down[e], swiglu_limit)
             d_wg[owner][e], d_wu[owner][e], d_wd[owner][e] = g_wg, g_wu, g_wd

@@ -69,6 +69,22 @@ def run(rank: int, world: int, port: int) -> None:
             assert torch.equal(out, out2), "output not bitwise reproducible"
             for name, a, b in zip(FIELDS, grads, grads2):
                 assert torch.equal(a, b), f"{name} not bitwise reproducible"
+
+            # the same layer in MXFP8 against the oracle that quantizes at the same points (rel-L2 <= 3e-2)
+            emu = O.moe_layer_oracle(inputs, swiglu_limit=limit, mxfp8=True)[rank]
+            qg = mok.ops.mxfp8_quantize(mine["w_routed_gate"], True, True)
+            qu = mok.ops.mxfp8_quantize(mine["w_routed_up"], True, True)
+            qd = mok.ops.mxfp8_quantize(mine["w_routed_down"], True, True)
+            sched = F.build_schedule(ws, config, mine["topk_experts"], num_local_experts=e_loc)
+            out8, ctx8 = F.forward(config, ws, sched, mine["x"], mine["router_weights"], *weights[:3], (qg[0], qg[1]),
+                                   (qu[0], qu[1]), (qd[0], qd[1]), swiglu_limit=limit)
+            grads8 = F.backward(config, ws, sched, ctx8, mine["d_output"], mine["x"], mine["router_weights"], *weights[:3],
+                                qg, qu, (qd[2], qd[3]), swiglu_limit=limit)
+            torch.cuda.synchronize()
+            mok.ops.check_status(dev)
+            for name, got in (("output", out8),) + tuple(zip(FIELDS, grads8)):
+                _, _, l2, _ = O.error_stats(getattr(emu, name).float(), got.float().cpu())
+                assert l2 <= 3e-2, (rank, "mxfp8", name, l2)
             F.clear_workspace_cache()
         dist.barrier()
         if rank == 0:
