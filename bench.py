@@ -254,6 +254,49 @@ def time_gemm_forms_mxfp8(dev, w, e_loc, sched, qg, qd, rows_buf):
     return out, rows_done
 
 
+def time_comm_kernels(dev, w, ws, sched, rows_buf, world, num_comm_ctas):
+    """Dispatch (pull rows from the owning ranks) and combine (push rows into the owners' slot buffers) alone, timed
+    with CUDA events while every rank does the same: GB/s of payload per rank and direction."""
+    import torch
+    import torch.distributed as dist
+    from mok import _native as nat
+    H, K, T = w["H"], w["K"], w["T"]
+    valid_rows = int((sched.peer_rank >= 0).sum().item())
+    padded_rows = int(sched.num_tokens.item())
+    rows_buf = min(rows_buf, (padded_rows + 255) // 256 * 256)
+    buf = torch.empty(rows_buf, H, device=dev, dtype=torch.bfloat16)
+    L = nat.lib()
+    st = nat.status_word(dev)
+    xp, cp = nat.ptr_array(ws.x_buffer_ptrs), nat.ptr_array(ws.combine_buffer_ptrs)
+    common = (nat.ptr(sched.peer_rank), nat.ptr(sched.peer_token_idx), nat.ptr(sched.num_tokens), 0, rows_buf, K, T, H)
+
+    def dispatch(ctas):
+        return L.mok_dispatch_rows(xp, None, world, *common, nat.ptr(buf), None, ctas, nat.ptr(st), nat.stream_ptr(dev))
+
+    def combine(ctas):
+        return L.mok_combine_rows(cp, None, world, *common, nat.ptr(buf), None, ctas, nat.ptr(st), nat.stream_ptr(dev))
+    out = {}
+    rows_done = min(valid_rows, rows_buf)
+    for name, fn, ctas in (("dispatch_full_grid", dispatch, 0), ("combine_full_grid", combine, 0),
+                           ("dispatch_comm_ctas", dispatch, num_comm_ctas), ("combine_comm_ctas", combine, num_comm_ctas)):
+        nat.check(fn(ctas), name)
+        dist.barrier()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(3):
+            fn(ctas)
+        e1.record()
+        torch.cuda.synchronize()
+        ms = torch.tensor([e0.elapsed_time(e1) / 3], device=dev, dtype=torch.float64)
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        gbs = rows_done * H * 2 / (ms.item() * 1e-3) / 1e9
+        out[name] = {"ms": ms.item(), "payload_gbs": gbs, "nvlink_gbs": gbs * (world - 1) / world}
+    dist.barrier()
+    nat.check_status(dev)
+    return out
+
+
 def run_gpu_arm(args, w):
     import torch
     import torch.distributed as dist
@@ -351,6 +394,7 @@ def run_gpu_arm(args, w):
         forms, rows_done = time_gemm_forms_mxfp8(dev, w, e_loc, sched, qg, qd, mb)
     else:
         forms, rows_done = time_gemm_forms(dev, w, e_loc, sched, weights, mb)
+    comm = time_comm_kernels(dev, w, ws, sched, mb, world, config.fwd_num_comm_sms * 8)
     if rank == 0:
         peaks = measured_peaks()
         tokens = T * world
@@ -377,7 +421,7 @@ def run_gpu_arm(args, w):
                          "achieved": dominant["tflops"], "peak": peak_tc, "unit": "TFLOP/s", "frac": dominant["tflops"] / peak_tc,
                          "traffic": traffic, "peak_source": peak_src, "rows": rows_done, "forms": forms},
             "e2e": {"value": tokens / (ms_e2e * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
-            "gpu_launches": int(launches), "clocks": clocks,
+            "gpu_launches": int(launches), "clocks": clocks, "comm": comm,
         }
         if world == 1 and not args.no_cpu:
             ct, ce = cpu_sample_size(w)

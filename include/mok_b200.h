@@ -106,6 +106,28 @@ int mok_barrier_all(int32_t* local_counter, const uint64_t* peer_counters, int e
                     uint32_t* status, int timeout_ms, mok_stream_t stream);
 
 /*
+ * Token dispatch alone: dst[row - row_begin, :] = src_ptrs[peer_rank[row]][peer_token_idx[row] / topk, :] for schedule
+ * rows [row_begin, min(row_end, *num_tokens)); padding rows become zeros.  With weight_ptrs != NULL each row is
+ * multiplied by the fp32 router weight weight_ptrs[peer][peer_token_idx[row]] (rounded to bf16) and the weight is
+ * stored in row_weight.  Replaces: dispatch_kernel, csrc/megakernel/dispatch_combine.cuh:1-150, and
+ * preload_router_weights_kernel, csrc/megakernel/utils.cuh:15-48.  num_ctas <= 0 fills the GPU.
+ */
+int mok_dispatch_rows(const uint64_t* src_ptrs, const uint64_t* weight_ptrs, int ep_size, const int32_t* peer_rank,
+                      const int32_t* peer_token_idx, const int32_t* num_tokens, int row_begin, int row_end, int topk,
+                      int num_local_tokens, int hidden, void* dst, float* row_weight, int num_ctas, uint32_t* status,
+                      mok_stream_t stream);
+
+/*
+ * Combine alone: dst_ptrs[peer_rank[row]][peer_token_idx[row], :] = src[row - row_begin, :] for non-padding rows, and
+ * with row_scalar != NULL also scalar_ptrs[peer][peer_token_idx[row]] = row_scalar[row - row_begin].  Every route owns
+ * its slot, so no atomics and no ordering dependence.  Replaces: combine_kernel, dispatch_combine.cuh:152-266.
+ */
+int mok_combine_rows(const uint64_t* dst_ptrs, const uint64_t* scalar_ptrs, int ep_size, const int32_t* peer_rank,
+                     const int32_t* peer_token_idx, const int32_t* num_tokens, int row_begin, int row_end, int topk,
+                     int num_local_tokens, int hidden, const void* src, const float* row_scalar, int num_ctas,
+                     uint32_t* status, mok_stream_t stream);
+
+/*
  * out[t] = bf16(y_shared[t] + sum_k w[t,k] * combine[t*K+k]) with k ascending in fp32.
  * Replaces: fwd_epilogue_kernel, csrc/utils.cuh:43-95 (op mok/ops.py:1279-1313).  y_shared may be NULL (treated as 0).
  */

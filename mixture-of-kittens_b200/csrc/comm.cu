@@ -229,3 +229,27 @@ extern "C" int mok_barrier_all(int32_t* local_counter, const uint64_t* peer_coun
     MOK_LAUNCH_CHECK("barrier_kernel");
     return MOK_OK;
 }
+
+extern "C" int mok_dispatch_rows(const uint64_t* src_ptrs, const uint64_t* weight_ptrs, int ep_size, const int32_t* peer_rank,
+                                 const int32_t* peer_token_idx, const int32_t* num_tokens, int row_begin, int row_end, int topk,
+                                 int num_local_tokens, int hidden, void* dst, float* row_weight, int num_ctas, uint32_t* status,
+                                 mok_stream_t stream) {
+    if (peer_rank == nullptr || peer_token_idx == nullptr || num_tokens == nullptr || dst == nullptr || topk <= 0 ||
+        num_local_tokens <= 0 || (weight_ptrs != nullptr && row_weight == nullptr))
+        return MOK_ERR_INVALID_ARGUMENT;
+    const mok::RowWindow w{peer_rank, peer_token_idx, num_tokens, row_begin, row_end, status};
+    return mok::launch_dispatch(src_ptrs, weight_ptrs, ep_size, w, topk, num_local_tokens, hidden, dst, row_weight, num_ctas,
+                                reinterpret_cast<cudaStream_t>(stream));
+}
+
+extern "C" int mok_combine_rows(const uint64_t* dst_ptrs, const uint64_t* scalar_ptrs, int ep_size, const int32_t* peer_rank,
+                                const int32_t* peer_token_idx, const int32_t* num_tokens, int row_begin, int row_end, int topk,
+                                int num_local_tokens, int hidden, const void* src, const float* row_scalar, int num_ctas,
+                                uint32_t* status, mok_stream_t stream) {
+    if (peer_rank == nullptr || peer_token_idx == nullptr || num_tokens == nullptr || src == nullptr || topk <= 0 ||
+        num_local_tokens <= 0)
+        return MOK_ERR_INVALID_ARGUMENT;
+    const mok::RowWindow w{peer_rank, peer_token_idx, num_tokens, row_begin, row_end, status};
+    return mok::launch_combine(dst_ptrs, scalar_ptrs, ep_size, w, topk, num_local_tokens, hidden, src, row_scalar, num_ctas,
+                               reinterpret_cast<cudaStream_t>(stream));
+}

@@ -243,6 +243,40 @@ __device__ __forceinline__ void mbar_arrive_leader(uint32_t bar) {
     asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(bar & kPairLeaderMask) : "memory");
 }
 
+// ---- GEMM epilogue staging -----------------------------------------------------------------------------------
+// After tcgen05.ld a thread holds 64 consecutive fp32 columns of ONE accumulator row; written straight to global
+// memory a warp would touch 32 rows with 16 bytes each per store instruction.  Each epilogue warp therefore owns a
+// small shared-memory patch (32 rows x 128 B, rows padded to 144 B so both access patterns are conflict free):
+// rows are written there as bf16, read back four rows per instruction, and stored as full 128-byte lines.
+constexpr int kEpiRowPitch = 144;
+constexpr int kEpiWarpBytes = 32 * kEpiRowPitch;
+
+__device__ __forceinline__ uint4 pack8_bf16(const uint32_t* f) {
+    return make_uint4(pack_bf16x2(__uint_as_float(f[0]), __uint_as_float(f[1])), pack_bf16x2(__uint_as_float(f[2]), __uint_as_float(f[3])),
+                      pack_bf16x2(__uint_as_float(f[4]), __uint_as_float(f[5])), pack_bf16x2(__uint_as_float(f[6]), __uint_as_float(f[7])));
+}
+
+// v0 / v1: columns [0,32) / [32,64) of this lane's row.  row0_out: global address of the warp's first row at the
+// first of the 64 columns; rows are ldd elements apart.
+__device__ __forceinline__ void epilogue_store_64cols(uint8_t* warp_patch, const uint32_t (&v0)[32], const uint32_t (&v1)[32],
+                                                      __nv_bfloat16* row0_out, long long ldd, int lane) {
+    uint4* mine = reinterpret_cast<uint4*>(warp_patch + lane * kEpiRowPitch);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        mine[i] = pack8_bf16(&v0[8 * i]);
+        mine[4 + i] = pack8_bf16(&v1[8 * i]);
+    }
+    __syncwarp();
+    const int seg = lane & 7;
+#pragma unroll
+    for (int it = 0; it < 8; ++it) {
+        const int r = it * 4 + (lane >> 3);
+        const uint4 w = *reinterpret_cast<const uint4*>(warp_patch + r * kEpiRowPitch + seg * 16);
+        *reinterpret_cast<uint4*>(row0_out + static_cast<long long>(r) * ldd + seg * 8) = w;
+    }
+    __syncwarp();
+}
+
 // Shared-memory matrix descriptor for a 128-byte-swizzled operand tile whose base is 1024-byte aligned.
 // Fields (Blackwell): start address >> 4 at bit 0, leading byte offset >> 4 at bit 16, stride byte offset >> 4
 // at bit 32, descriptor version 1 at bit 46, layout type 2 (128B swizzle) at bit 61.

@@ -59,7 +59,8 @@ struct SharedLayout {
     static constexpr int kTmemEmpty = kTmemFull + 8;
     static constexpr int kTmemPtr = kTmemEmpty + 8;
     static constexpr int kAbort = kTmemPtr + 4;
-    static constexpr int kCum = kAbort + 4 + 8;
+    static constexpr int kEpilogue = (kAbort + 4 + 127) / 128 * 128;   // 4 warps x 32 rows x 144 B staging patches
+    static constexpr int kCum = kEpilogue + 4 * kEpiWarpBytes;
 };
 
 template <int MODE>
@@ -303,12 +304,20 @@ mxfp8_gemm_kernel(const __grid_constant__ MapSet ms0, const __grid_constant__ Ma
                 out = p.D0 + static_cast<long long>(tile.expert) * p.d_expert_stride +
                       static_cast<long long>(tile.m0 + row_in_tile) * p.ldd + tile.n0;
             const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
+            uint8_t* patch = smem_gen + SharedLayout::kEpilogue + quarter * kEpiWarpBytes;
+            bf16* warp_out = out - static_cast<long long>(lane) * p.ldd;
 #pragma unroll 1
-            for (int c = 0; c < BN / 32; ++c) {
-                uint32_t v[32];
-                tmem_ld_32x32(taddr + c * 32, v);
+            for (int c = 0; c < BN / 64; ++c) {
+                uint32_t v0[32], v1[32];
+                tmem_ld_32x32(taddr + c * 64, v0);
+                tmem_ld_32x32(taddr + c * 64 + 32, v1);
                 tmem_ld_wait();
-                store_row_chunk(out + c * 32, v, tile.accumulate != 0);
+                if (tile.accumulate) {
+                    store_row_chunk(out + c * 64, v0, true);
+                    store_row_chunk(out + c * 64 + 32, v1, true);
+                } else {
+                    epilogue_store_64cols(patch, v0, v1, warp_out + c * 64, p.ldd, lane);
+                }
             }
             tc_fence_before_sync();
             __syncwarp();

@@ -79,6 +79,12 @@ def lib() -> ctypes.CDLL:
                                             c_int, c_void_p, c_void_p]
         L.mok_grouped_wgrad_bf16.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
                                              c_void_p, c_void_p]
+        L.mok_dispatch_rows.argtypes = [POINTER(c_uint64), POINTER(c_uint64), c_int, c_void_p, c_void_p, c_void_p, c_int, c_int,
+                                        c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p]
+        L.mok_combine_rows.argtypes = [POINTER(c_uint64), POINTER(c_uint64), c_int, c_void_p, c_void_p, c_void_p, c_int, c_int,
+                                       c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p]
+        L.mok_dispatch_rows.restype = c_int
+        L.mok_combine_rows.restype = c_int
         L.mok_grouped_gemm_mxfp8.argtypes = [c_void_p] * 7 + [c_int] * 4 + [c_void_p, c_void_p]
         L.mok_grouped_wgrad_mxfp8.argtypes = [c_void_p] * 7 + [c_int] * 4 + [c_void_p, c_void_p]
         L.mok_grouped_gemm_mxfp8.restype = c_int

@@ -89,6 +89,39 @@ def test_layer_with_recomputed_context_and_bitwise_repeat(dist_ctx):
         assert torch.equal(a, b), f"{name} is not bitwise reproducible"
 
 
+def test_dispatch_and_combine_permutations_are_bit_exact(dist_ctx):
+    """x_routed[row] must be the token row the schedule names (zeros on padding rows) and combine_buffer[token*K+k] the
+    expert output row of that route — copies, so bit for bit."""
+    import torch.distributed as dist
+    import mok
+    F = mok.functional
+    _, _, dev = dist_ctx
+    E, H, I, K, T = 8, 256, 256, 4, 512
+    config = F.MoKConfig(minibatch_size=256, macrobatch_size=4096)
+    inp = O.make_rank_inputs(0, E, E, K, T, H, I)
+    d = _to(dev, inp)
+    ws = F.get_workspace(config, dist.group.WORLD, device=dev, num_local_tokens=T, hidden_size=H, topk=K)
+    sched = F.build_schedule(ws, config, d["topk_experts"], num_local_experts=E)
+    ws.x_buffer.copy_(d["x"])
+    outs = mok.ops.dispatch_mlp_swiglu_combine_fwd_bf16(
+        ws.x_buffer, ws.x_buffer_ptrs, ws.combine_buffer, ws.combine_buffer_ptrs, d["w_shared_gate"], d["w_routed_gate"],
+        d["w_shared_up"], d["w_routed_up"], d["w_shared_down"], d["w_routed_down"], sched.peer_rank, sched.peer_token_idx,
+        sched.num_tokens, sched.tokens_per_expert, K, None, config.fwd_num_comm_sms, config.macrobatch_size, config.minibatch_size)
+    x_routed, y_routed = outs[0], outs[8]
+    torch.cuda.synchronize()
+    n = int(sched.num_tokens.item())
+    peer, route = sched.peer_rank[:n].long(), sched.peer_token_idx[:n].long()
+    valid = peer >= 0
+    expect = torch.zeros(n, H, dtype=torch.bfloat16, device=dev)
+    expect[valid] = d["x"][route[valid] // K]
+    assert torch.equal(x_routed[:n], expect)
+    assert int(valid.sum()) == T * K                                  # every route scheduled exactly once
+    assert torch.equal(ws.combine_buffer[route[valid]], y_routed[:n][valid])
+    # the schedule the rows follow is the oracle's, bit for bit
+    pr, pt, nt, _ = O.schedule_oracle(inp.topk_experts.to(torch.int32).unsqueeze(0).numpy(), E, ws.schedule_capacity, 0)
+    assert (sched.peer_rank.cpu().numpy() == pr).all() and (sched.peer_token_idx.cpu().numpy() == pt).all() and n == int(nt[0])
+
+
 def test_chunked_two_stream_pipeline_equals_single_stream(dist_ctx, monkeypatch):
     """Dispatch / combine on the internal stream with many small chunks gives bit-identical results to the plain
     single-stream order (same kernels, same per-element arithmetic)."""
