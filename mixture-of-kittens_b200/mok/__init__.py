@@ -3,7 +3,8 @@ backward) over `mok.ops` (twelve `torch.ops.mok.*` custom ops) over libmok_b200.
 from . import ops
 from . import _fake_impls  # noqa: F401  (registers shape functions for torch.compile / FakeTensor)
 from . import functional
+from .module import MoKMoE, moe_layer
 
 __version__ = "0.1.0"
 
-__all__ = ["__version__", "functional", "ops"]
+__all__ = ["__version__", "functional", "ops", "MoKMoE", "moe_layer"]

@@ -229,6 +229,13 @@ def get_workspace(config: MoKConfig, group: dist.ProcessGroup, *, device: torch.
     return workspace
 
 
+def _stage(buffer: torch.Tensor, value: torch.Tensor) -> None:
+    """Copies an input into its symmetric buffer unless the caller already produced it there (pass the workspace
+    buffer itself as the argument to skip the copy; the reference marks these copies as removable, :509,:709-711)."""
+    if value.data_ptr() != buffer.data_ptr():
+        buffer.copy_(value)
+
+
 def _barrier(workspace: MoKWorkspace) -> None:
     barrier_all(workspace.barrier_buffer, workspace.barrier_buffer_ptrs, workspace.barrier_buffer_multicast_ptr,
                 workspace.barrier_target)
@@ -324,8 +331,8 @@ def forward(config: MoKConfig, workspace: MoKWorkspace, schedule: MoKSchedule, x
             swiglu_limit: float | None = None) -> tuple[torch.Tensor, MoKForwardContext]:
     """MoE forward (reference :470-568).  Returns (output bf16 [T, H], forward context for backward)."""
     validate_inputs(config, workspace, schedule, x, router_weights)
-    workspace.x_buffer.copy_(x)
-    workspace.router_weight_buffer.copy_(router_weights)
+    _stage(workspace.x_buffer, x)
+    _stage(workspace.router_weight_buffer, router_weights)
     _barrier(workspace)   # every peer's x is in place before anyone pulls
 
     sched = (schedule.peer_rank, schedule.peer_token_idx, schedule.num_tokens, schedule.tokens_per_expert)
@@ -366,7 +373,7 @@ def recompute_forward_context(config: MoKConfig, workspace: MoKWorkspace, schedu
         raise TypeError("routed gate and up weights must use the same precision representation")
     if isinstance(routed_gate_weights, tuple) and (len(routed_gate_weights) != 2 or len(routed_up_weights) != 2):
         raise ValueError("MXFP8 routed gate and up weights must be data/scale pairs")
-    workspace.x_buffer.copy_(x)
+    _stage(workspace.x_buffer, x)
     _barrier(workspace)
 
     sched = (schedule.peer_rank, schedule.peer_token_idx, schedule.num_tokens, schedule.tokens_per_expert)
@@ -402,9 +409,9 @@ def backward(config: MoKConfig, workspace: MoKWorkspace, schedule: MoKSchedule, 
     validate_inputs(config, workspace, schedule, x, router_weights, grad_output)
     if not isinstance(forward_context, MoKForwardContext):
         raise TypeError("forward_context must be a MoKForwardContext")
-    workspace.d_y_buffer.copy_(grad_output)
-    workspace.x_buffer.copy_(x)
-    workspace.router_weight_buffer.copy_(router_weights)
+    _stage(workspace.d_y_buffer, grad_output)
+    _stage(workspace.x_buffer, x)
+    _stage(workspace.router_weight_buffer, router_weights)
     _barrier(workspace)
 
     bufs = (workspace.d_y_buffer, workspace.d_y_buffer_ptrs, workspace.d_x_routed_buffer, workspace.d_x_routed_buffer_ptrs,
