@@ -388,7 +388,13 @@ def run_gpu_arm(args, w):
     h2d = sum(t.numel() * t.element_size() for t in (hx, hdy, htopk, hrw))
     d2h = sum(t.numel() * t.element_size() for t in (hout, hdx, hdrw))
 
+    tracing = os.environ.get("MOK_TRACE") == "1"
+    if tracing:   # drop what the earlier steps recorded, keep the timeline of exactly one step
+        mok.ops.lib().mok_trace_dump(os.devnull.encode())
     sched, out, grads = step(x, dy, topk, rw)
+    if tracing:
+        os.makedirs(os.path.join(ROOT, "gpurun_out"), exist_ok=True)
+        mok.ops.lib().mok_trace_dump(os.path.join(ROOT, "gpurun_out", f"trace_{args.dtype}_ep{world}_rank{rank}.txt").encode())
     del out, grads
     if mxfp8:
         forms, rows_done = time_gemm_forms_mxfp8(dev, w, e_loc, sched, qg, qd, mb)

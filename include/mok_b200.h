@@ -50,6 +50,11 @@ const char* mok_last_error(void);
 /* Kernels this library has launched in this process so far (all threads). */
 long long mok_launch_count(void);
 
+/* Debugging aid: with MOK_TRACE=1 in the environment the layer entry points time their phases (pull / compute /
+ * push per chunk, wgrad, shared expert) with CUDA events; this call synchronises the device, writes one line per
+ * phase ("name chunk stream start_ms end_ms") to `path` and clears the record. */
+int mok_trace_dump(const char* path);
+
 /* Bytes of int32 scratch `mok_schedule` needs for these sizes. */
 int64_t mok_schedule_scratch_bytes(int ep_size, int num_local_tokens, int topk, int num_local_experts);
 

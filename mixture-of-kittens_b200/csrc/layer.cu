@@ -14,7 +14,10 @@
 //     main:            wait d[c] -> GEMMs(c) -> record y[c]
 // Dispatch runs two chunks ahead.  The internal stream is forked from and joined back into the caller's stream
 // inside every call, so the caller sees ordinary stream semantics.  No kernel ever spins on another kernel.
+#include <stdio.h>
 #include <stdlib.h>
+
+#include <vector>
 
 #include "comm.cuh"
 #include "elementwise.cuh"
@@ -71,6 +74,36 @@ int order_after(DeviceStreams* d, cudaStream_t signaller, cudaStream_t waiter) {
     MOK_CUDA_CHECK(cudaEventRecord(e, signaller));
     MOK_CUDA_CHECK(cudaStreamWaitEvent(waiter, e, 0));
     return MOK_OK;
+}
+
+// ---- optional phase timeline (MOK_TRACE=1): CUDA events around every pull / compute / push / wgrad phase ---------
+struct TraceRecord {
+    const char* name;
+    int chunk;
+    int on_comm_stream;
+    cudaEvent_t begin, end;
+};
+std::vector<TraceRecord>& trace_records() {
+    static std::vector<TraceRecord> records;
+    return records;
+}
+bool trace_enabled() {
+    static const bool on = [] {
+        const char* v = getenv("MOK_TRACE");
+        return v != nullptr && v[0] == '1';
+    }();
+    return on;
+}
+int trace_begin(const char* name, int chunk, bool on_comm, cudaStream_t st) {
+    if (!trace_enabled()) return -1;
+    TraceRecord r{name, chunk, on_comm ? 1 : 0, nullptr, nullptr};
+    if (cudaEventCreate(&r.begin) != cudaSuccess || cudaEventCreate(&r.end) != cudaSuccess) return -1;
+    cudaEventRecord(r.begin, st);
+    trace_records().push_back(r);
+    return static_cast<int>(trace_records().size()) - 1;
+}
+void trace_end(int index, cudaStream_t st) {
+    if (index >= 0) cudaEventRecord(trace_records()[index].end, st);
 }
 
 bool overlap_enabled() {
@@ -327,17 +360,23 @@ int run_chunks(const mok_layer_args* a, const Span& win, bool overlapped, Device
     for (int step = 0; step < n + 2; ++step) {
         const int c = step, m = step - 1, k = step - 2;
         if (c < n) {
+            const int t = trace_begin("pull", c, true, d->comm);
             MOK_TRY(pull(span_of(c), ctas, d->comm));
+            trace_end(t, d->comm);
             MOK_CUDA_CHECK(cudaEventRecord(pulled[c % 3], d->comm));
         }
         if (m >= 0 && m < n) {
             MOK_CUDA_CHECK(cudaStreamWaitEvent(main_stream, pulled[m % 3], 0));
+            const int t = trace_begin("compute", m, false, main_stream);
             MOK_TRY(compute(span_of(m), main_stream));
+            trace_end(t, main_stream);
             MOK_CUDA_CHECK(cudaEventRecord(computed[m % 3], main_stream));
         }
         if (k >= 0 && k < n) {
             MOK_CUDA_CHECK(cudaStreamWaitEvent(d->comm, computed[k % 3], 0));
+            const int t = trace_begin("push", k, true, d->comm);
             MOK_TRY(push(span_of(k), ctas, d->comm));
+            trace_end(t, d->comm);
         }
     }
     return MOK_OK;
@@ -420,7 +459,11 @@ extern "C" int mok_moe_backward_bf16(const mok_layer_args* a, mok_stream_t strea
         MOK_TRY(order_after(d, s, d->comm));
     }
 
-    if (shared) MOK_TRY(shared_backward(a, s));
+    if (shared) {
+        const int ts = trace_begin("shared_bwd", 0, false, s);
+        MOK_TRY(shared_backward(a, s));
+        trace_end(ts, s);
+    }
 
     float* row_weight = a->row_scratch;
     float* row_grad = a->row_scratch + a->macrobatch_size;
@@ -453,9 +496,11 @@ extern "C" int mok_moe_backward_bf16(const mok_layer_args* a, mok_stream_t strea
             }));
         // weight gradients over the whole window (fixed K order = schedule order), while the last pushes drain
         const GemmProblem p = routed_problem(a, win);
+        const int tw = trace_begin("wgrad", wi, false, s);
         MOK_TRY(launch_wgrad_gemm(p, a->d_y_routed, H, a->hidden_routed, I, a->d_w_routed_down, s));
         MOK_TRY(launch_wgrad_gemm(p, a->d_gate_routed, I, a->x_routed, H, a->d_w_routed_gate, s));
         MOK_TRY(launch_wgrad_gemm(p, a->d_up_routed, I, a->x_routed, H, a->d_w_routed_up, s));
+        trace_end(tw, s);
         if (overlapped) {
             MOK_TRY(order_after(d, d->comm, s));
             if (wi + 1 < num_windows(a)) MOK_TRY(order_after(d, s, d->comm));
@@ -549,7 +594,11 @@ extern "C" int mok_moe_backward_mxfp8(const mok_layer_args* a, mok_stream_t stre
         MOK_TRY(streams_for_current_device(&d));
         MOK_TRY(order_after(d, s, d->comm));
     }
-    if (shared) MOK_TRY(shared_backward(a, s));
+    if (shared) {
+        const int ts = trace_begin("shared_bwd", 0, false, s);
+        MOK_TRY(shared_backward(a, s));
+        trace_end(ts, s);
+    }
 
     const Fp8Operand wd_t = weight_operand(a, a->w_down_t_fp8, a->w_down_t_sc, I, H);   // [E, I, H]: N = I, K = H
     const Fp8Operand wg_t = weight_operand(a, a->w_gate_t_fp8, a->w_gate_t_sc, H, I);   // [E, H, I]: N = H, K = I
@@ -610,5 +659,33 @@ extern "C" int mok_moe_backward_mxfp8(const mok_layer_args* a, mok_stream_t stre
     }
     MOK_TRY(launch_zero_empty_wgrads(a->tokens_per_expert, a->num_local_experts, a->d_w_routed_gate, a->d_w_routed_up,
                                      a->d_w_routed_down, static_cast<long long>(H) * I, s));
+    return MOK_OK;
+}
+
+// Writes the phase timeline collected under MOK_TRACE=1 (one line per phase: name, chunk, stream, start and end in
+// milliseconds since the first phase) and clears it.  Synchronises the device: a debugging aid, not for hot paths.
+extern "C" int mok_trace_dump(const char* path) {
+    using namespace mok;
+    std::vector<TraceRecord>& recs = trace_records();
+    if (path == nullptr) return MOK_ERR_INVALID_ARGUMENT;
+    MOK_CUDA_CHECK(cudaDeviceSynchronize());
+    FILE* f = fopen(path, "w");
+    if (f == nullptr) return MOK_ERR_INVALID_ARGUMENT;
+    for (size_t i = 0; i < recs.size(); ++i) {
+        float t0 = 0.f, t1 = 0.f;
+        const cudaError_t e0 = cudaEventElapsedTime(&t0, recs[0].begin, recs[i].begin);
+        const cudaError_t e1 = cudaEventElapsedTime(&t1, recs[0].begin, recs[i].end);
+        if (e0 != cudaSuccess || e1 != cudaSuccess)
+            fprintf(f, "# %s %d: %s / %s\n", recs[i].name, recs[i].chunk, cudaGetErrorName(e0), cudaGetErrorName(e1));
+        else
+            fprintf(f, "%s %d %s %.4f %.4f\n", recs[i].name, recs[i].chunk, recs[i].on_comm_stream ? "comm" : "main", t0, t1);
+    }
+    for (size_t i = 0; i < recs.size(); ++i) {
+        cudaEventDestroy(recs[i].begin);
+        cudaEventDestroy(recs[i].end);
+    }
+    fclose(f);
+    recs.clear();
+    (void)cudaGetLastError();   // a failed query above must not surface in the next launch check
     return MOK_OK;
 }

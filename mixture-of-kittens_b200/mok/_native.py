@@ -79,6 +79,8 @@ def lib() -> ctypes.CDLL:
                                             c_int, c_void_p, c_void_p]
         L.mok_grouped_wgrad_bf16.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
                                              c_void_p, c_void_p]
+        L.mok_trace_dump.argtypes = [c_char_p]
+        L.mok_trace_dump.restype = c_int
         L.mok_dispatch_rows.argtypes = [POINTER(c_uint64), POINTER(c_uint64), c_int, c_void_p, c_void_p, c_void_p, c_int, c_int,
                                         c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p]
         L.mok_combine_rows.argtypes = [POINTER(c_uint64), POINTER(c_uint64), c_int, c_void_p, c_void_p, c_void_p, c_int, c_int,
