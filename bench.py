@@ -62,22 +62,24 @@ class ClockSampler:
     def start(self):
         try:
             self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
-                                          "-i", str(self.index), "-lms", "200"], stdout=subprocess.PIPE, text=True)
+                                          "-i", str(self.index), "-lms", "100"], stdout=subprocess.PIPE, text=True)
             threading.Thread(target=self._read, daemon=True).start()
         except OSError:
             self.proc = None
 
     def _read(self):
         for line in self.proc.stdout:
-            self.samples.append([c.strip() for c in line.split(",")])
+            self.samples.append((time.time(), [c.strip() for c in line.split(",")]))
 
-    def stop(self):
+    def stop(self, t_begin: float = 0.0, t_end: float = float("inf")):
+        """Summarises the samples that arrived inside [t_begin, t_end] (wall clock); all of them by default."""
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": []}
         self.proc.terminate()
         time.sleep(0.05)
         clocks, reasons, mx = [], set(), None
-        for s in self.samples:
+        inside = [s for t, s in self.samples if t_begin <= t <= t_end + 0.2]
+        for s in inside or [s for _, s in self.samples[-2:]]:
             try:
                 clocks.append(float(s[0]))
                 mx = float(s[1])
@@ -359,17 +361,19 @@ def run_gpu_arm(args, w):
         dist.all_reduce(ms, op=dist.ReduceOp.MAX)
         return ms.item() / steps
 
+    sampler = ClockSampler(local)   # started before the warm-up so that it is already reporting in the timed region
+    sampler.start()
     for _ in range(args.warmup):
         out = step(x, dy, topk, rw)
         del out
     torch.cuda.synchronize()
     mok.ops.check_status(dev)
-    sampler = ClockSampler(local)
-    sampler.start()
     launches0 = mok.ops.lib().mok_launch_count()
+    t_begin = time.time()
     ms_step = timed(lambda: step(x, dy, topk, rw), args.steps)
+    t_end = time.time()
     launches = (mok.ops.lib().mok_launch_count() - launches0) // args.steps
-    clocks = sampler.stop()
+    clocks = sampler.stop(t_begin, t_end)
     mok.ops.check_status(dev)
 
     # end to end: host buffers in, results back to the host, every step
@@ -387,6 +391,21 @@ def run_gpu_arm(args, w):
     ms_e2e = timed(e2e_step, max(1, min(args.steps, 3)))
     h2d = sum(t.numel() * t.element_size() for t in (hx, hdy, htopk, hrw))
     d2h = sum(t.numel() * t.element_size() for t in (hout, hdx, hdrw))
+
+    # where one step spends its time: CUDA events between the three public calls (one extra, untimed step)
+    marks = [torch.cuda.Event(enable_timing=True) for _ in range(4)]
+    torch.cuda.synchronize()
+    marks[0].record()
+    sched_p = F.build_schedule(ws, config, topk, num_local_experts=e_loc)
+    marks[1].record()
+    out_p, ctx_p = F.forward(config, ws, sched_p, x, rw, *fwd_w)
+    marks[2].record()
+    grads_p = F.backward(config, ws, sched_p, ctx_p, dy, x, rw, *bwd_w)
+    marks[3].record()
+    torch.cuda.synchronize()
+    phases = {"build_schedule_ms": marks[0].elapsed_time(marks[1]), "forward_ms": marks[1].elapsed_time(marks[2]),
+              "backward_ms": marks[2].elapsed_time(marks[3])}
+    del sched_p, out_p, ctx_p, grads_p
 
     tracing = os.environ.get("MOK_TRACE") == "1"
     if tracing:   # drop what the earlier steps recorded, keep the timeline of exactly one step
@@ -427,7 +446,7 @@ def run_gpu_arm(args, w):
                          "achieved": dominant["tflops"], "peak": peak_tc, "unit": "TFLOP/s", "frac": dominant["tflops"] / peak_tc,
                          "traffic": traffic, "peak_source": peak_src, "rows": rows_done, "forms": forms},
             "e2e": {"value": tokens / (ms_e2e * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
-            "gpu_launches": int(launches), "clocks": clocks, "comm": comm,
+            "gpu_launches": int(launches), "clocks": clocks, "comm": comm, "phases": phases,
         }
         if world == 1 and not args.no_cpu:
             ct, ce = cpu_sample_size(w)
@@ -458,7 +477,11 @@ def run_gemm_only(args, w):
     g = torch.Generator(device=dev).manual_seed(0)
     wt = lambda *s: torch.randn(*s, generator=g, device=dev, dtype=torch.bfloat16).mul_(w["std"])  # noqa: E731
     weights = (None, None, None, wt(e, I, H), None, wt(e, H, I))
-    forms, rows_done = time_gemm_forms(dev, w, e, sched, weights, rows)
+    if args.dtype == "mxfp8":
+        qg = mok.ops.mxfp8_quantize(weights[3], True, False)
+        forms, rows_done = time_gemm_forms_mxfp8(dev, w, e, sched, qg, None, rows)
+    else:
+        forms, rows_done = time_gemm_forms(dev, w, e, sched, weights, rows)
     peaks = measured_peaks()
     print(json.dumps({"mode": "gemm-only", "rows": rows_done, "experts": e, "hidden": H, "intermediate": I, "forms": forms,
                       "peak_burst_tflops": peaks["burst"], "peak_source": peaks["source"]}), flush=True)

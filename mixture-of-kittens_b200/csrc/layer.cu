@@ -205,7 +205,15 @@ GemmProblem shared_problem(const mok_layer_args* a) {
     return p;
 }
 
-int comm_ctas(const mok_layer_args* a, bool overlapped) { return overlapped ? a->num_comm_sms * 8 : 0; }
+// CTAs of a dispatch / combine launch that runs beside the GEMMs: num_comm_sms x 8 (MOK_COMM_CTAS overrides, for tuning)
+int comm_ctas(const mok_layer_args* a, bool overlapped) {
+    if (!overlapped) return 0;
+    if (const char* v = getenv("MOK_COMM_CTAS")) {
+        const int n = atoi(v);
+        if (n > 0) return n;
+    }
+    return a->num_comm_sms * 8;
+}
 
 // ---- per-span building blocks ---------------------------------------------------------------------------
 int dispatch_x(const mok_layer_args* a, const Span& s, int ctas, cudaStream_t st) {

@@ -277,6 +277,23 @@ __device__ __forceinline__ void epilogue_store_64cols(uint8_t* warp_patch, const
     __syncwarp();
 }
 
+// Same, for 64 columns that are already packed to bf16 (8 x 16 bytes of this lane's row).
+__device__ __forceinline__ void epilogue_store_packed_64cols(uint8_t* warp_patch, const uint4* row_vectors, __nv_bfloat16* row0_out,
+                                                             long long ldd, int lane) {
+    uint4* mine = reinterpret_cast<uint4*>(warp_patch + lane * kEpiRowPitch);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) mine[i] = row_vectors[i];
+    __syncwarp();
+    const int seg = lane & 7;
+#pragma unroll
+    for (int it = 0; it < 8; ++it) {
+        const int r = it * 4 + (lane >> 3);
+        const uint4 w = *reinterpret_cast<const uint4*>(warp_patch + r * kEpiRowPitch + seg * 16);
+        *reinterpret_cast<uint4*>(row0_out + static_cast<long long>(r) * ldd + seg * 8) = w;
+    }
+    __syncwarp();
+}
+
 // Shared-memory matrix descriptor for a 128-byte-swizzled operand tile whose base is 1024-byte aligned.
 // Fields (Blackwell): start address >> 4 at bit 0, leading byte offset >> 4 at bit 16, stride byte offset >> 4
 // at bit 32, descriptor version 1 at bit 46, layout type 2 (128B swizzle) at bit 61.

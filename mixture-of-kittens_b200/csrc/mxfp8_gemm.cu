@@ -306,22 +306,35 @@ mxfp8_gemm_kernel(const __grid_constant__ MapSet ms0, const __grid_constant__ Ma
             const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
             uint8_t* patch = smem_gen + SharedLayout::kEpilogue + quarter * kEpiWarpBytes;
             bf16* warp_out = out - static_cast<long long>(lane) * p.ldd;
+            if (tile.accumulate) {   // rare (later windows of a multi-window backward): add in fp32 per row
 #pragma unroll 1
-            for (int c = 0; c < BN / 64; ++c) {
-                uint32_t v0[32], v1[32];
-                tmem_ld_32x32(taddr + c * 64, v0);
-                tmem_ld_32x32(taddr + c * 64 + 32, v1);
-                tmem_ld_wait();
-                if (tile.accumulate) {
-                    store_row_chunk(out + c * 64, v0, true);
-                    store_row_chunk(out + c * 64 + 32, v1, true);
-                } else {
-                    epilogue_store_64cols(patch, v0, v1, warp_out + c * 64, p.ldd, lane);
+                for (int c = 0; c < BN / 32; ++c) {
+                    uint32_t v[32];
+                    tmem_ld_32x32(taddr + c * 32, v);
+                    tmem_ld_wait();
+                    store_row_chunk(out + c * 32, v, true);
                 }
+                tc_fence_before_sync();
+                __syncwarp();
+                if (lane == 0) mbar_arrive_leader(bar_tmem_empty);
+            } else {
+                // The accumulator is single-buffered: read the whole row into registers as packed bf16 first and hand
+                // tensor memory back to the MMA issuer before any of it is written out.
+                uint4 packed[BN / 8];
+#pragma unroll
+                for (int c = 0; c < BN / 32; ++c) {
+                    uint32_t v[32];
+                    tmem_ld_32x32(taddr + c * 32, v);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) packed[c * 4 + i] = pack8_bf16(&v[8 * i]);
+                }
+                tc_fence_before_sync();
+                __syncwarp();
+                if (lane == 0) mbar_arrive_leader(bar_tmem_empty);
+#pragma unroll
+                for (int c = 0; c < BN / 64; ++c) epilogue_store_packed_64cols(patch, &packed[c * 8], warp_out + c * 64, p.ldd, lane);
             }
-            tc_fence_before_sync();
-            __syncwarp();
-            if (lane == 0) mbar_arrive_leader(bar_tmem_empty);
             ++iter;
         }
     }
