@@ -480,6 +480,20 @@ def run_gemm_only(args, w):
     if args.dtype == "mxfp8":
         qg = mok.ops.mxfp8_quantize(weights[3], True, False)
         forms, rows_done = time_gemm_forms_mxfp8(dev, w, e, sched, qg, None, rows)
+        # the quantizer on a [4 * rows, H] activation-sized matrix (bf16 in, e4m3 + scales out in both layouts)
+        act = torch.randn(4 * rows, H, generator=g, device=dev, dtype=torch.bfloat16)
+        for both in (False, True):
+            mok.ops.mxfp8_quantize(act, True, both)
+            ev = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
+            torch.cuda.synchronize()
+            ev[0].record()
+            for _ in range(5):
+                mok.ops.mxfp8_quantize(act, True, both)
+            ev[1].record()
+            torch.cuda.synchronize()
+            ms = ev[0].elapsed_time(ev[1]) / 5
+            nbytes = act.numel() * (2 + (2 if both else 1) * (1 + 1 / 32))
+            forms["quantize_" + ("both_layouts" if both else "normal")] = {"ms": ms, "hbm_gbs": nbytes / (ms * 1e-3) / 1e9}
     else:
         forms, rows_done = time_gemm_forms(dev, w, e, sched, weights, rows)
     peaks = measured_peaks()

@@ -232,7 +232,7 @@ def get_workspace(config: MoKConfig, group: dist.ProcessGroup, *, device: torch.
 def _stage(buffer: torch.Tensor, value: torch.Tensor) -> None:
     """Copies an input into its symmetric buffer unless the caller already produced it there (pass the workspace
     buffer itself as the argument to skip the copy; the reference marks these copies as removable, :509,:709-711)."""
-    if value.data_ptr() != buffer.data_ptr():
+    if value is not buffer:
         buffer.copy_(value)
 
 

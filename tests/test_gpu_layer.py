@@ -161,6 +161,34 @@ def test_moe_module_trains_one_step(dist_ctx):
     assert x.grad is not None and torch.isfinite(x.grad.float()).all()
 
 
+def test_forward_backward_trace_as_one_graph(dist_ctx):
+    """The ops are opaque custom ops with shape functions, so `torch.compile(fullgraph=True)` captures the whole
+    forward + backward call sequence (the reference pins this, tests/test_misc.py:1262-1521); the compiled function
+    returns what the eager one returns."""
+    import torch.distributed as dist
+    import mok
+    F = mok.functional
+    _, _, dev = dist_ctx
+    E, H, I, K, T = 4, 256, 256, 2, 512
+    config = F.MoKConfig(minibatch_size=256, macrobatch_size=1024)
+    inp = O.make_rank_inputs(0, E, E, K, T, H, I)
+    d = _to(dev, inp)
+    ws = F.get_workspace(config, dist.group.WORLD, device=dev, num_local_tokens=T, hidden_size=H, topk=K)
+    weights = (d["w_shared_gate"], d["w_shared_up"], d["w_shared_down"], d["w_routed_gate"], d["w_routed_up"], d["w_routed_down"])
+
+    def layer(x, top_experts, rw, d_out):
+        sched = F.build_schedule(ws, config, top_experts, num_local_experts=E)
+        out, ctx = F.forward(config, ws, sched, x, rw, *weights)
+        grads = F.backward(config, ws, sched, ctx, d_out, x, rw, *weights)
+        return out, grads[0], grads[1], grads[2]
+
+    eager = layer(d["x"], d["topk_experts"], d["router_weights"], d["d_output"])
+    compiled = torch.compile(layer, backend="eager", fullgraph=True)(d["x"], d["topk_experts"], d["router_weights"], d["d_output"])
+    torch.cuda.synchronize()
+    for a, b in zip(eager, compiled):
+        assert torch.equal(a, b)
+
+
 def test_chunked_two_stream_pipeline_equals_single_stream(dist_ctx, monkeypatch):
     """Dispatch / combine on the internal stream with many small chunks gives bit-identical results to the plain
     single-stream order (same kernels, same per-element arithmetic)."""
