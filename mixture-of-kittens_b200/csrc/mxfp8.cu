@@ -17,6 +17,21 @@ namespace {
 
 constexpr int kTile = 128;
 constexpr int kRowPitch = kTile * 2 + 16;   // bytes; the 16-byte pad keeps row-wise 16 B reads conflict free
+constexpr int kOutPitch = kTile + 16;       // bytes per staged e4m3 output row
+constexpr int kQuantSmemBytes = kTile * (kRowPitch + kOutPitch);
+
+int enable_quantize_smem();   // raises the kernel's dynamic shared-memory limit once per device
+
+// 128 rows x 128 bytes from the staging tile to global memory, eight lanes per row: every store instruction of a
+// warp writes four complete 128-byte lines (a thread writing its own row would touch 32 lines with 16 bytes each).
+__device__ __forceinline__ void store_staged_rows(const uint8_t* otile, uint8_t* out, long long ld, int tid) {
+#pragma unroll 4
+    for (int i = tid; i < kTile * 8; i += 128) {
+        const int r = i >> 3, seg = i & 7;
+        *reinterpret_cast<uint4*>(out + static_cast<long long>(r) * ld + seg * 16) =
+            *reinterpret_cast<const uint4*>(otile + r * kOutPitch + seg * 16);
+    }
+}
 
 struct QuantArgs {
     const bf16* x;             // row 0 of the span / matrix 0
@@ -35,7 +50,9 @@ struct QuantArgs {
 };
 
 __global__ void __launch_bounds__(128) quantize_kernel(const QuantArgs a) {
-    __shared__ __align__(16) uint8_t tile[kTile * kRowPitch];
+    extern __shared__ __align__(16) uint8_t quant_smem[];
+    uint8_t* tile = quant_smem;                                  // bf16 input tile, padded rows
+    uint8_t* otile = quant_smem + kTile * kRowPitch;             // e4m3 rows staged for full-line stores
     const int tid = threadIdx.x;
     const int tc = blockIdx.x, tr = blockIdx.y, e = blockIdx.z;
     const int limit = a.num_tokens != nullptr ? min(a.row_end, *a.num_tokens) : a.row_end;
@@ -52,7 +69,8 @@ __global__ void __launch_bounds__(128) quantize_kernel(const QuantArgs a) {
 
     if (a.q != nullptr) {   // thread = row of the tile, four blocks of 32 along the row
         uint32_t scale_word = 0;
-        uint8_t* out = a.q + e * a.q_mat_stride + (static_cast<long long>(tr) * kTile + tid) * a.x_ld + static_cast<long long>(tc) * kTile;
+        uint8_t* out = a.q + e * a.q_mat_stride + static_cast<long long>(tr) * kTile * a.x_ld + static_cast<long long>(tc) * kTile;
+        uint8_t* mine = otile + tid * kOutPitch;
 #pragma unroll
         for (int kb = 0; kb < 4; ++kb) {
             uint32_t packed[16];
@@ -64,15 +82,19 @@ __global__ void __launch_bounds__(128) quantize_kernel(const QuantArgs a) {
             uint32_t out8[8], sbyte;
             mxfp8_quantize_block(packed, out8, sbyte);
             scale_word |= sbyte << (kb * 8);
-            *reinterpret_cast<uint4*>(out + kb * 32) = make_uint4(out8[0], out8[1], out8[2], out8[3]);
-            *reinterpret_cast<uint4*>(out + kb * 32 + 16) = make_uint4(out8[4], out8[5], out8[6], out8[7]);
+            *reinterpret_cast<uint4*>(mine + kb * 32) = make_uint4(out8[0], out8[1], out8[2], out8[3]);
+            *reinterpret_cast<uint4*>(mine + kb * 32 + 16) = make_uint4(out8[4], out8[5], out8[6], out8[7]);
         }
+        __syncthreads();
+        store_staged_rows(otile, out, a.x_ld, tid);
+        __syncthreads();
         uint8_t* sdst = a.sc + e * a.sc_mat_stride + tr * a.sc_row_tile_stride + static_cast<long long>(tc) * 512;
         *reinterpret_cast<uint32_t*>(sdst + (tid & 31) * 16 + (tid >> 5) * 4) = scale_word;
     }
     if (a.qt != nullptr) {  // thread = column of the tile = row of the transpose, four blocks of 32 down the column
         uint32_t scale_word = 0;
-        uint8_t* out = a.qt + e * a.qt_mat_stride + (static_cast<long long>(tc) * kTile + tid) * a.qt_ld + static_cast<long long>(tr) * kTile;
+        uint8_t* out = a.qt + e * a.qt_mat_stride + static_cast<long long>(tc) * kTile * a.qt_ld + static_cast<long long>(tr) * kTile;
+        uint8_t* mine = otile + tid * kOutPitch;
 #pragma unroll
         for (int kb = 0; kb < 4; ++kb) {
             uint32_t packed[16];
@@ -85,9 +107,11 @@ __global__ void __launch_bounds__(128) quantize_kernel(const QuantArgs a) {
             uint32_t out8[8], sbyte;
             mxfp8_quantize_block(packed, out8, sbyte);
             scale_word |= sbyte << (kb * 8);
-            *reinterpret_cast<uint4*>(out + kb * 32) = make_uint4(out8[0], out8[1], out8[2], out8[3]);
-            *reinterpret_cast<uint4*>(out + kb * 32 + 16) = make_uint4(out8[4], out8[5], out8[6], out8[7]);
+            *reinterpret_cast<uint4*>(mine + kb * 32) = make_uint4(out8[0], out8[1], out8[2], out8[3]);
+            *reinterpret_cast<uint4*>(mine + kb * 32 + 16) = make_uint4(out8[4], out8[5], out8[6], out8[7]);
         }
+        __syncthreads();
+        store_staged_rows(otile, out, a.qt_ld, tid);
         uint8_t* sdst = a.sct + e * a.sct_mat_stride + tc * a.sct_row_tile_stride + static_cast<long long>(tr) * 512;
         *reinterpret_cast<uint32_t*>(sdst + (tid & 31) * 16 + (tid >> 5) * 4) = scale_word;
     }
@@ -127,6 +151,18 @@ __global__ void __launch_bounds__(256) dequantize_kernel(const uint8_t* __restri
     }
 }
 
+int enable_quantize_smem() {
+    static bool done[16] = {false};
+    int dev = 0;
+    MOK_CUDA_CHECK(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 16) return MOK_ERR_UNSUPPORTED;
+    if (!done[dev]) {
+        MOK_CUDA_CHECK(cudaFuncSetAttribute(quantize_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kQuantSmemBytes));
+        done[dev] = true;
+    }
+    return MOK_OK;
+}
+
 }  // namespace
 
 int launch_quantize_rows(const void* x, int cols, const int32_t* num_tokens, int row_begin, int row_end, void* q, void* sc,
@@ -152,7 +188,8 @@ int launch_quantize_rows(const void* x, int cols, const int32_t* num_tokens, int
     const int row_tiles = (row_end - row_begin) / 128;
     if (row_tiles > 65535) return MOK_ERR_TOO_LARGE;
     dim3 grid(cols / 128, row_tiles, 1);
-    quantize_kernel<<<grid, 128, 0, stream>>>(a);
+    if (int rc = enable_quantize_smem()) return rc;
+    quantize_kernel<<<grid, 128, kQuantSmemBytes, stream>>>(a);
     MOK_LAUNCH_CHECK("mxfp8_quantize_kernel");
     return MOK_OK;
 }
@@ -202,7 +239,8 @@ extern "C" int mok_mxfp8_quantize(const void* x_bf16, int num_matrices, int rows
     a.row_begin = 0;
     a.row_end = rows;
     dim3 grid(cols / 128, rows / 128, num_matrices);
-    quantize_kernel<<<grid, 128, 0, reinterpret_cast<cudaStream_t>(stream)>>>(a);
+    if (int rc = enable_quantize_smem()) return rc;
+    quantize_kernel<<<grid, 128, kQuantSmemBytes, reinterpret_cast<cudaStream_t>(stream)>>>(a);
     MOK_LAUNCH_CHECK("mxfp8_quantize_kernel");
     return MOK_OK;
 }
