@@ -17,52 +17,20 @@
 //   rows / B [E,K,N]   D[r,:] = sum_s A_s[r,:] B_s[e]  dgrad down; dgrad gate+up (2 sets) (B MN-major)
 //   wgrad              D[e] (+)= A[rows_e,:]^T B[rows_e,:], K = rows of expert e          (A, B MN-major)
 // Every output element has exactly one writer and a fixed K order, so results are run-to-run identical.
-#include "grouped_gemm.cuh"
+#include "gemm_tiles.cuh"
 
 namespace mok {
 namespace {
 
-constexpr int BM = 256;                              // tile rows of the CTA pair
-constexpr int BM_CTA = 128;                          // rows each CTA stages and accumulates
-constexpr int BN = 256;
-constexpr int BN_CTA = 128;                          // B columns each CTA stages
+using namespace tiles;
+
 constexpr int BK = 64;
 constexpr int STAGES = 6;
 constexpr int A_TILE_BYTES = BM_CTA * BK * 2;        // 16 KB
 constexpr int B_TILE_BYTES = BN_CTA * BK * 2;        // 16 KB
 constexpr int STAGE_BYTES = A_TILE_BYTES + B_TILE_BYTES;
 constexpr int CHUNK_BYTES = 64 * BK * 2;             // one 64(MN) x 64(K) block of an MN-major operand: 8 KB
-constexpr int NUM_THREADS = 192;
-constexpr int TMEM_COLS = 512;
-constexpr int MODE_ROWS = 0;
-constexpr int MODE_WGRAD = 1;
 
-struct KernelParams {
-    const int32_t* tokens_per_expert;
-    const int32_t* num_tokens;
-    int num_experts;
-    int dense_rows;
-    int row_begin, row_end;
-    int n_blocks;     // rows: N / 256 per output set; wgrad: N / 256
-    int m_blocks_w;   // wgrad: M / 256
-    int k_blocks;     // rows: K / 64 per operand set
-    int n_sets;       // rows: output sets sharing A (1 or 2)
-    int k_sets;       // rows: operand sets accumulated into one output (1 or 2)
-    bf16* D0;
-    bf16* D1;
-    long long ldd;
-    long long d_expert_stride;
-    uint32_t* status;
-};
-
-struct Tile {
-    int expert;
-    int row0;       // rows: first schedule row of the tile; wgrad: first K row
-    int m0, n0;     // wgrad: output row / column offset; rows: n0 = column offset
-    int set;        // rows: output set
-    int k_blocks;   // K steps of 64
-    int accumulate; // wgrad: add to what is already stored
-};
 
 struct SharedLayout {
     // dynamic shared memory, 1024-byte aligned base (identical in both CTAs of a pair):
@@ -78,68 +46,6 @@ struct SharedLayout {
     static constexpr int kCum = kEpilogue + 4 * kEpiWarpBytes;    // (E + 1) x 4 B
 };
 
-template <int MODE>
-__device__ __forceinline__ bool decode_tile(const KernelParams& p, const int* cum, int lo, int hi, int t, Tile& tile) {
-    if (MODE == MODE_ROWS) {
-        const int per_m = p.n_blocks * p.n_sets;
-        const int mt = t / per_m;
-        const int rem = t - mt * per_m;
-        tile.set = rem / p.n_blocks;
-        tile.n0 = (rem - tile.set * p.n_blocks) * BN;
-        tile.row0 = lo + mt * BM;
-        tile.m0 = 0;
-        int e = 0;
-        if (p.tokens_per_expert != nullptr) {   // largest e with cum[e] <= row0
-            int a = 0, b = p.num_experts;
-            while (b - a > 1) {
-                const int mid = (a + b) >> 1;
-                if (cum[mid] <= tile.row0) a = mid; else b = mid;
-            }
-            e = a;
-        }
-        tile.expert = e;
-        tile.k_blocks = p.k_blocks * p.k_sets;
-        tile.accumulate = 0;
-        return true;
-    } else {
-        const int per_e = p.m_blocks_w * p.n_blocks;
-        const int e = t / per_e;
-        const int rem = t - e * per_e;
-        const int mi = rem / p.n_blocks;
-        tile.expert = e;
-        tile.m0 = mi * BM;
-        tile.n0 = (rem - mi * p.n_blocks) * BN;
-        tile.set = 0;
-        const int ks = max(cum[e], lo);
-        const int ke = min(cum[e + 1], hi);
-        tile.row0 = ks;
-        tile.k_blocks = ke > ks ? (ke - ks) / BK : 0;
-        tile.accumulate = cum[e] < lo ? 1 : 0;
-        return tile.k_blocks > 0;
-    }
-}
-
-__device__ __forceinline__ void store_row_chunk(bf16* dst, const uint32_t (&acc)[32], bool accumulate) {
-    uint4* out = reinterpret_cast<uint4*>(dst);
-#pragma unroll
-    for (int v = 0; v < 4; ++v) {
-        float f[8];
-#pragma unroll
-        for (int i = 0; i < 8; ++i) f[i] = __uint_as_float(acc[v * 8 + i]);
-        if (accumulate) {
-            const uint4 old = out[v];
-            const float2 o0 = unpack_bf16x2(old.x), o1 = unpack_bf16x2(old.y), o2 = unpack_bf16x2(old.z), o3 = unpack_bf16x2(old.w);
-            f[0] += o0.x; f[1] += o0.y; f[2] += o1.x; f[3] += o1.y;
-            f[4] += o2.x; f[5] += o2.y; f[6] += o3.x; f[7] += o3.y;
-        }
-        uint4 w;
-        w.x = pack_bf16x2(f[0], f[1]);
-        w.y = pack_bf16x2(f[2], f[3]);
-        w.z = pack_bf16x2(f[4], f[5]);
-        w.w = pack_bf16x2(f[6], f[7]);
-        out[v] = w;
-    }
-}
 
 template <int MODE, bool B_MN>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
@@ -187,25 +93,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_const
         tmem_alloc_pair(smem_u32(const_cast<uint32_t*>(tmem_ptr_slot)), TMEM_COLS);
         tmem_relinquish_pair();
     }
-    if (warp == 2) {   // inclusive prefix of the per-expert row counts -> cum[0..E]
-        if (p.tokens_per_expert == nullptr) {
-            if (lane == 0) { cum[0] = 0; cum[1] = p.dense_rows; }
-        } else {
-            int carry = 0;
-            if (lane == 0) cum[0] = 0;
-            for (int base = 0; base < p.num_experts; base += 32) {
-                const int idx = base + lane;
-                int v = idx < p.num_experts ? p.tokens_per_expert[idx] : 0;
-#pragma unroll
-                for (int off = 1; off < 32; off <<= 1) {
-                    const int n = __shfl_up_sync(0xffffffffu, v, off);
-                    if (lane >= off) v += n;
-                }
-                if (idx < p.num_experts) cum[idx + 1] = carry + v;
-                carry += __shfl_sync(0xffffffffu, v, 31);
-            }
-        }
-    }
+    if (warp == 2) expert_row_prefix(p, cum, lane);   // cum[0..E]: first schedule row of every expert
     tc_fence_before_sync();
     __syncthreads();
     cluster_sync_all();     // both CTAs' barriers exist before either one signals the other
@@ -215,9 +103,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_const
     const int total_rows = p.tokens_per_expert == nullptr ? p.dense_rows : *p.num_tokens;
     const int lo = p.row_begin;
     const int hi = min(p.row_end, total_rows);
-    int total_tiles;
-    if (MODE == MODE_ROWS) total_tiles = hi > lo ? ((hi - lo) / BM) * p.n_blocks * p.n_sets : 0;
-    else total_tiles = hi > lo ? p.num_experts * p.m_blocks_w * p.n_blocks : 0;
+    const int num_tiles = total_tiles<MODE>(p, lo, hi);
 
     constexpr uint32_t kIdesc = umma_idesc_bf16(BM, BN, A_MN, B_MN);
 
@@ -226,9 +112,9 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_const
         int stage = 0;
         uint32_t phase = 0;
         bool ok = true;
-        for (int t = pair; t < total_tiles && ok; t += num_pairs) {
+        for (int t = pair; t < num_tiles && ok; t += num_pairs) {
             Tile tile;
-            if (!decode_tile<MODE>(p, cum, lo, hi, t, tile)) continue;
+            if (!decode_tile<MODE, BK>(p, cum, lo, hi, t, tile)) continue;
             for (int kb = 0; kb < tile.k_blocks; ++kb) {
                 ok = mbar_wait(bar_empty + 8 * stage, phase ^ 1u, abort_flag, p.status);
                 if (!ok) break;
@@ -276,9 +162,9 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_const
             // two 8-row groups (2 KB) of an MN-major tile
             constexpr uint32_t kAStep = A_MN ? 128u : 2u;
             constexpr uint32_t kBStep = B_MN ? 128u : 2u;
-            for (int t = pair; t < total_tiles && ok; t += num_pairs) {
+            for (int t = pair; t < num_tiles && ok; t += num_pairs) {
                 Tile tile;
-                if (!decode_tile<MODE>(p, cum, lo, hi, t, tile)) continue;
+                if (!decode_tile<MODE, BK>(p, cum, lo, hi, t, tile)) continue;
                 const int acc = iter & 1;
                 const uint32_t acc_phase = (iter >> 1) & 1u;
                 ok = mbar_wait(bar_tmem_empty + 8 * acc, acc_phase ^ 1u, abort_flag, p.status);
@@ -312,9 +198,9 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_const
         const int row_in_tile = cta_rank * BM_CTA + quarter * 32 + lane;
         int iter = 0;
         bool ok = true;
-        for (int t = pair; t < total_tiles && ok; t += num_pairs) {
+        for (int t = pair; t < num_tiles && ok; t += num_pairs) {
             Tile tile;
-            if (!decode_tile<MODE>(p, cum, lo, hi, t, tile)) continue;
+            if (!decode_tile<MODE, BK>(p, cum, lo, hi, t, tile)) continue;
             const int acc = iter & 1;
             const uint32_t acc_phase = (iter >> 1) & 1u;
             ok = mbar_wait(bar_tmem_full + 8 * acc, acc_phase, abort_flag, p.status);
@@ -365,113 +251,27 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_const
 // ---------------------------------------------------------------------------------------------------------
 // Host side
 // ---------------------------------------------------------------------------------------------------------
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
-                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiledFn encode_fn() {
-    static EncodeTiledFn fn = nullptr;
-    if (fn == nullptr) {
-        void* sym = nullptr;
-        cudaDriverEntryPointQueryResult qres;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres) == cudaSuccess &&
-            qres == cudaDriverEntryPointSuccess)
-            fn = reinterpret_cast<EncodeTiledFn>(sym);
-    }
-    return fn;
-}
 
 // Rank-4 bf16 map over a row-major [d2][d1][d0] array (d0 contiguous); box = {b0, b1, 1, 1}.
 int make_map(CUtensorMap* map, const void* base, uint64_t d0, uint64_t d1, uint64_t d2, uint32_t b0, uint32_t b1) {
-    EncodeTiledFn fn = encode_fn();
-    if (fn == nullptr) {
-        set_last_error("cuTensorMapEncodeTiled unavailable", cudaErrorNotSupported);
-        return MOK_ERR_CUDA;
-    }
-    cuuint64_t dims[4] = {d0, d1, d2, 1};
-    cuuint64_t strides[3] = {d0 * 2, d0 * d1 * 2, d0 * d1 * d2 * 2};
-    cuuint32_t box[4] = {b0, b1, 1, 1};
-    cuuint32_t estr[4] = {1, 1, 1, 1};
-    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), dims, strides, box, estr,
-                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS) {
-        set_last_error("cuTensorMapEncodeTiled failed", cudaErrorInvalidValue);
-        return MOK_ERR_CUDA;
-    }
-    return MOK_OK;
+    const cuuint64_t dims[4] = {d0, d1, d2, 1};
+    const cuuint64_t strides[3] = {d0 * 2, d0 * d1 * 2, d0 * d1 * d2 * 2};
+    const cuuint32_t box[4] = {b0, b1, 1, 1};
+    return encode_map(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, base, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
 }
 
 size_t smem_bytes(int num_experts) {
     return 1024 + SharedLayout::kCum + 4 * (static_cast<size_t>(num_experts) + 2);
 }
 
-constexpr int kMaxDynamicSmem = 232448 - 1024;
-
 template <int MODE, bool B_MN>
 int launch(const CUtensorMap& a0, const CUtensorMap& b0, const CUtensorMap& a1, const CUtensorMap& b1,
            const KernelParams& kp, int max_tiles, cudaStream_t stream) {
-    auto kernel = grouped_gemm_kernel<MODE, B_MN>;
-    const size_t smem = smem_bytes(kp.num_experts);
-    static int max_pairs[16] = {0};   // per device: CTA pairs that can be resident at once
-    int dev = 0;
-    MOK_CUDA_CHECK(cudaGetDevice(&dev));
-    if (dev < 0 || dev >= 16) return MOK_ERR_UNSUPPORTED;
-
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = 2;
-    attr[0].val.clusterDim.y = 1;
-    attr[0].val.clusterDim.z = 1;
-    cudaLaunchConfig_t cfg = {};
-    cfg.blockDim = dim3(NUM_THREADS);
-    cfg.dynamicSmemBytes = smem;
-    cfg.stream = stream;
-    cfg.attrs = attr;
-    cfg.numAttrs = 1;
-
-    if (max_pairs[dev] == 0) {
-        MOK_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxDynamicSmem));
-        cfg.gridDim = dim3(2 * sm_count());
-        cfg.dynamicSmemBytes = kMaxDynamicSmem;
-        int clusters = 0;
-        MOK_CUDA_CHECK(cudaOccupancyMaxActiveClusters(&clusters, kernel, &cfg));
-        cfg.dynamicSmemBytes = smem;
-        max_pairs[dev] = clusters > 0 ? clusters : sm_count() / 2;
-    }
-    int pairs = max_pairs[dev];
-    if (max_tiles < pairs) pairs = max_tiles;
-    if (pairs <= 0) return MOK_OK;
-    cfg.gridDim = dim3(2 * pairs);
-    cudaError_t err = cudaLaunchKernelEx(&cfg, kernel, a0, b0, a1, b1, kp);
-    if (err != cudaSuccess) return fail_cuda("grouped_gemm_kernel launch", err);
-    MOK_LAUNCH_CHECK("grouped_gemm_kernel");
-    return MOK_OK;
+    static int resident_pairs[16] = {0};
+    return launch_pairs(grouped_gemm_kernel<MODE, B_MN>, "grouped_gemm_kernel", resident_pairs, smem_bytes(kp.num_experts),
+                        max_tiles, stream, a0, b0, a1, b1, kp);
 }
 
-int check_problem(const GemmProblem& pb) {
-    if (pb.num_experts < 1 || pb.num_experts > MOK_MAX_LOCAL_EXPERTS) return MOK_ERR_TOO_LARGE;
-    if (pb.row_begin < 0 || pb.row_end < pb.row_begin || (pb.row_begin % BM) != 0 || (pb.row_end % BM) != 0)
-        return MOK_ERR_INVALID_ARGUMENT;
-    if (pb.buffer_rows <= 0) return MOK_ERR_INVALID_ARGUMENT;
-    if (pb.tokens_per_expert == nullptr && (pb.num_experts != 1 || pb.dense_rows % BM != 0)) return MOK_ERR_INVALID_ARGUMENT;
-    if (pb.tokens_per_expert != nullptr && pb.num_tokens == nullptr) return MOK_ERR_INVALID_ARGUMENT;
-    return MOK_OK;
-}
-
-KernelParams base_params(const GemmProblem& pb) {
-    KernelParams kp{};
-    kp.tokens_per_expert = pb.tokens_per_expert;
-    kp.num_tokens = pb.num_tokens;
-    kp.num_experts = pb.num_experts;
-    kp.dense_rows = pb.dense_rows;
-    kp.row_begin = pb.row_begin;
-    kp.row_end = pb.row_end;
-    kp.n_sets = 1;
-    kp.k_sets = 1;
-    kp.status = pb.status;
-    return kp;
-}
 
 }  // namespace
 

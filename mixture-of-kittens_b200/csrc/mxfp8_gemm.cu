@@ -8,12 +8,14 @@
 // Tensor memory: 256 accumulator columns + 12 scale columns, so the accumulator is single-buffered.
 // Both operands are K-major; the dgrad and wgrad forms use transposed-quantized copies of weights / activations
 // (the role MXFP8 plays in the reference grouped GEMM, csrc/megakernel/grouped_gemm.cuh:222-249).
+#include "gemm_tiles.cuh"
 #include "mxfp8_gemm.cuh"
 
 namespace mok {
 namespace {
 
-constexpr int BM = 256, BM_CTA = 128, BN = 256, BN_CTA = 128;
+using namespace tiles;
+
 constexpr int BK = 128;                               // e4m3 elements = bytes per K step
 constexpr int STAGES = 6;
 constexpr int A_TILE_BYTES = BM_CTA * BK;             // 16 KB
@@ -22,34 +24,9 @@ constexpr int DATA_STAGE_BYTES = A_TILE_BYTES + B_TILE_BYTES;
 constexpr int SCALE_TILE_BYTES = 512;
 constexpr int SCALE_STAGE_BYTES = 3 * SCALE_TILE_BYTES;   // A rows of this CTA, B columns [0,128), B columns [128,256)
 constexpr int STAGE_TX_BYTES = DATA_STAGE_BYTES + SCALE_STAGE_BYTES;
-constexpr int NUM_THREADS = 192;
-constexpr int TMEM_COLS = 512;
 constexpr int TMEM_SFA_COL = 256;                     // 4 columns
 constexpr int TMEM_SFB_COL = 260;                     // 8 columns
-constexpr int MODE_ROWS = 0;
-constexpr int MODE_WGRAD = 1;
 
-struct KernelParams {
-    const int32_t* tokens_per_expert;
-    const int32_t* num_tokens;
-    int num_experts;
-    int dense_rows;
-    int row_begin, row_end;
-    int n_blocks;     // N / 256 (per output set in rows mode)
-    int m_blocks_w;   // wgrad: M / 256
-    int k_blocks;     // rows: K / 128 per operand set
-    int n_sets, k_sets;
-    int n_tiles_per_expert;   // rows: N / 128, scale row tiles of one expert's weight
-    bf16* D0;
-    bf16* D1;
-    long long ldd;
-    long long d_expert_stride;
-    uint32_t* status;
-};
-
-struct Tile {
-    int expert, row0, m0, n0, set, k_blocks, accumulate;
-};
 
 struct SharedLayout {
     static constexpr int kScales = STAGES * DATA_STAGE_BYTES;
@@ -63,68 +40,6 @@ struct SharedLayout {
     static constexpr int kCum = kEpilogue + 4 * kEpiWarpBytes;
 };
 
-template <int MODE>
-__device__ __forceinline__ bool decode_tile(const KernelParams& p, const int* cum, int lo, int hi, int t, Tile& tile) {
-    if (MODE == MODE_ROWS) {
-        const int per_m = p.n_blocks * p.n_sets;
-        const int mt = t / per_m;
-        const int rem = t - mt * per_m;
-        tile.set = rem / p.n_blocks;
-        tile.n0 = (rem - tile.set * p.n_blocks) * BN;
-        tile.row0 = lo + mt * BM;
-        tile.m0 = 0;
-        int e = 0;
-        if (p.tokens_per_expert != nullptr) {
-            int a = 0, b = p.num_experts;
-            while (b - a > 1) {
-                const int mid = (a + b) >> 1;
-                if (cum[mid] <= tile.row0) a = mid; else b = mid;
-            }
-            e = a;
-        }
-        tile.expert = e;
-        tile.k_blocks = p.k_blocks * p.k_sets;
-        tile.accumulate = 0;
-        return true;
-    } else {
-        const int per_e = p.m_blocks_w * p.n_blocks;
-        const int e = t / per_e;
-        const int rem = t - e * per_e;
-        const int mi = rem / p.n_blocks;
-        tile.expert = e;
-        tile.m0 = mi * BM;
-        tile.n0 = (rem - mi * p.n_blocks) * BN;
-        tile.set = 0;
-        const int ks = max(cum[e], lo);
-        const int ke = min(cum[e + 1], hi);
-        tile.row0 = ks;
-        tile.k_blocks = ke > ks ? (ke - ks) / BK : 0;
-        tile.accumulate = cum[e] < lo ? 1 : 0;
-        return tile.k_blocks > 0;
-    }
-}
-
-__device__ __forceinline__ void store_row_chunk(bf16* dst, const uint32_t (&acc)[32], bool accumulate) {
-    uint4* out = reinterpret_cast<uint4*>(dst);
-#pragma unroll
-    for (int v = 0; v < 4; ++v) {
-        float f[8];
-#pragma unroll
-        for (int i = 0; i < 8; ++i) f[i] = __uint_as_float(acc[v * 8 + i]);
-        if (accumulate) {
-            const uint4 old = out[v];
-            const float2 o0 = unpack_bf16x2(old.x), o1 = unpack_bf16x2(old.y), o2 = unpack_bf16x2(old.z), o3 = unpack_bf16x2(old.w);
-            f[0] += o0.x; f[1] += o0.y; f[2] += o1.x; f[3] += o1.y;
-            f[4] += o2.x; f[5] += o2.y; f[6] += o3.x; f[7] += o3.y;
-        }
-        uint4 w;
-        w.x = pack_bf16x2(f[0], f[1]);
-        w.y = pack_bf16x2(f[2], f[3]);
-        w.z = pack_bf16x2(f[4], f[5]);
-        w.w = pack_bf16x2(f[6], f[7]);
-        out[v] = w;
-    }
-}
 
 // One operand set: data and scale tensor maps of A and B.
 struct MapSet {
@@ -169,25 +84,7 @@ mxfp8_gemm_kernel(const __grid_constant__ MapSet ms0, const __grid_constant__ Ma
         tmem_alloc_pair(smem_u32(const_cast<uint32_t*>(tmem_ptr_slot)), TMEM_COLS);
         tmem_relinquish_pair();
     }
-    if (warp == 2) {
-        if (p.tokens_per_expert == nullptr) {
-            if (lane == 0) { cum[0] = 0; cum[1] = p.dense_rows; }
-        } else {
-            int carry = 0;
-            if (lane == 0) cum[0] = 0;
-            for (int base = 0; base < p.num_experts; base += 32) {
-                const int idx = base + lane;
-                int v = idx < p.num_experts ? p.tokens_per_expert[idx] : 0;
-#pragma unroll
-                for (int off = 1; off < 32; off <<= 1) {
-                    const int n = __shfl_up_sync(0xffffffffu, v, off);
-                    if (lane >= off) v += n;
-                }
-                if (idx < p.num_experts) cum[idx + 1] = carry + v;
-                carry += __shfl_sync(0xffffffffu, v, 31);
-            }
-        }
-    }
+    if (warp == 2) expert_row_prefix(p, cum, lane);
     tc_fence_before_sync();
     __syncthreads();
     cluster_sync_all();
@@ -197,18 +94,16 @@ mxfp8_gemm_kernel(const __grid_constant__ MapSet ms0, const __grid_constant__ Ma
     const int total_rows = p.tokens_per_expert == nullptr ? p.dense_rows : *p.num_tokens;
     const int lo = p.row_begin;
     const int hi = min(p.row_end, total_rows);
-    int total_tiles;
-    if (MODE == MODE_ROWS) total_tiles = hi > lo ? ((hi - lo) / BM) * p.n_blocks * p.n_sets : 0;
-    else total_tiles = hi > lo ? p.num_experts * p.m_blocks_w * p.n_blocks : 0;
+    const int num_tiles = total_tiles<MODE>(p, lo, hi);
 
     if (warp == 0) {
         // ---- TMA producer (both CTAs): data tiles and scale tiles of one K step land on the leader's barrier ----
         int stage = 0;
         uint32_t phase = 0;
         bool ok = true;
-        for (int t = pair; t < total_tiles && ok; t += num_pairs) {
+        for (int t = pair; t < num_tiles && ok; t += num_pairs) {
             Tile tile;
-            if (!decode_tile<MODE>(p, cum, lo, hi, t, tile)) continue;
+            if (!decode_tile<MODE, BK>(p, cum, lo, hi, t, tile)) continue;
             for (int kb = 0; kb < tile.k_blocks; ++kb) {
                 ok = mbar_wait(bar_empty + 8 * stage, phase ^ 1u, abort_flag, p.status);
                 if (!ok) break;
@@ -253,9 +148,9 @@ mxfp8_gemm_kernel(const __grid_constant__ MapSet ms0, const __grid_constant__ Ma
             bool ok = true;
             const uint32_t sfa_tmem = tmem_base + TMEM_SFA_COL;
             const uint32_t sfb_tmem = tmem_base + TMEM_SFB_COL;
-            for (int t = pair; t < total_tiles && ok; t += num_pairs) {
+            for (int t = pair; t < num_tiles && ok; t += num_pairs) {
                 Tile tile;
-                if (!decode_tile<MODE>(p, cum, lo, hi, t, tile)) continue;
+                if (!decode_tile<MODE, BK>(p, cum, lo, hi, t, tile)) continue;
                 ok = mbar_wait(bar_tmem_empty, (iter & 1u) ^ 1u, abort_flag, p.status);   // epilogue drained the accumulator
                 if (!ok) break;
                 tc_fence_after_sync();
@@ -291,9 +186,9 @@ mxfp8_gemm_kernel(const __grid_constant__ MapSet ms0, const __grid_constant__ Ma
         const int row_in_tile = cta_rank * BM_CTA + quarter * 32 + lane;
         int iter = 0;
         bool ok = true;
-        for (int t = pair; t < total_tiles && ok; t += num_pairs) {
+        for (int t = pair; t < num_tiles && ok; t += num_pairs) {
             Tile tile;
-            if (!decode_tile<MODE>(p, cum, lo, hi, t, tile)) continue;
+            if (!decode_tile<MODE, BK>(p, cum, lo, hi, t, tile)) continue;
             ok = mbar_wait(bar_tmem_full, iter & 1u, abort_flag, p.status);
             if (!ok) break;
             tc_fence_after_sync();
@@ -354,38 +249,6 @@ mxfp8_gemm_kernel(const __grid_constant__ MapSet ms0, const __grid_constant__ Ma
 // ---------------------------------------------------------------------------------------------------------
 // Host side
 // ---------------------------------------------------------------------------------------------------------
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
-                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiledFn encode_fn() {
-    static EncodeTiledFn fn = nullptr;
-    if (fn == nullptr) {
-        void* sym = nullptr;
-        cudaDriverEntryPointQueryResult qres;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres) == cudaSuccess &&
-            qres == cudaDriverEntryPointSuccess)
-            fn = reinterpret_cast<EncodeTiledFn>(sym);
-    }
-    return fn;
-}
-
-int encode(CUtensorMap* map, CUtensorMapDataType type, const void* base, const cuuint64_t (&dims)[4],
-           const cuuint64_t (&strides)[3], const cuuint32_t (&box)[4], CUtensorMapSwizzle swizzle) {
-    EncodeTiledFn fn = encode_fn();
-    if (fn == nullptr) {
-        set_last_error("cuTensorMapEncodeTiled unavailable", cudaErrorNotSupported);
-        return MOK_ERR_CUDA;
-    }
-    cuuint32_t estr[4] = {1, 1, 1, 1};
-    CUresult r = fn(map, type, 4, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle,
-                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS) {
-        set_last_error("cuTensorMapEncodeTiled failed (mxfp8)", cudaErrorInvalidValue);
-        return MOK_ERR_CUDA;
-    }
-    return MOK_OK;
-}
 
 // e4m3 bytes [groups][rows_per_group][k]: box 128 (K) x 128 (rows)
 int data_map(CUtensorMap* map, const Fp8Operand& op, long long rows_per_group, long long groups) {
@@ -394,7 +257,7 @@ int data_map(CUtensorMap* map, const Fp8Operand& op, long long rows_per_group, l
     const cuuint64_t strides[3] = {static_cast<cuuint64_t>(op.ld), static_cast<cuuint64_t>(op.ld * rows_per_group),
                                    static_cast<cuuint64_t>(op.ld * rows_per_group * groups)};
     const cuuint32_t box[4] = {BK, 128, 1, 1};
-    return encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, op.data, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
+    return encode_map(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, op.data, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
 }
 
 // scale tiles [row tile][K tile][128 words]: one 512-byte tile per copy
@@ -405,7 +268,7 @@ int scale_map(CUtensorMap* map, const Fp8Operand& op) {
     const cuuint64_t strides[3] = {512, static_cast<cuuint64_t>(op.scale_row_tile_stride),
                                    static_cast<cuuint64_t>(op.scale_row_tile_stride * row_tiles)};
     const cuuint32_t box[4] = {128, 1, 1, 1};
-    return encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT32, op.scales, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_NONE);
+    return encode_map(map, CU_TENSOR_MAP_DATA_TYPE_UINT32, op.scales, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_NONE);
 }
 
 bool operand_ok(const Fp8Operand& op) {
@@ -424,67 +287,13 @@ int fill_set(MapSet* ms, const Fp8Operand& a, long long a_groups, const Fp8Opera
 }
 
 size_t smem_bytes(int num_experts) { return 1024 + SharedLayout::kCum + 4 * (static_cast<size_t>(num_experts) + 2); }
-constexpr int kMaxDynamicSmem = 232448 - 1024;
-
 template <int MODE>
 int launch(const MapSet& ms0, const MapSet& ms1, const KernelParams& kp, int max_tiles, cudaStream_t stream) {
-    auto kernel = mxfp8_gemm_kernel<MODE>;
-    static int max_pairs[16] = {0};
-    int dev = 0;
-    MOK_CUDA_CHECK(cudaGetDevice(&dev));
-    if (dev < 0 || dev >= 16) return MOK_ERR_UNSUPPORTED;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = 2;
-    attr[0].val.clusterDim.y = 1;
-    attr[0].val.clusterDim.z = 1;
-    cudaLaunchConfig_t cfg = {};
-    cfg.blockDim = dim3(NUM_THREADS);
-    cfg.dynamicSmemBytes = smem_bytes(kp.num_experts);
-    cfg.stream = stream;
-    cfg.attrs = attr;
-    cfg.numAttrs = 1;
-    if (max_pairs[dev] == 0) {
-        MOK_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxDynamicSmem));
-        cfg.gridDim = dim3(2 * sm_count());
-        const size_t keep = cfg.dynamicSmemBytes;
-        cfg.dynamicSmemBytes = kMaxDynamicSmem;
-        int clusters = 0;
-        MOK_CUDA_CHECK(cudaOccupancyMaxActiveClusters(&clusters, kernel, &cfg));
-        cfg.dynamicSmemBytes = keep;
-        max_pairs[dev] = clusters > 0 ? clusters : sm_count() / 2;
-    }
-    int pairs = max_pairs[dev] < max_tiles ? max_pairs[dev] : max_tiles;
-    if (pairs <= 0) return MOK_OK;
-    cfg.gridDim = dim3(2 * pairs);
-    cudaError_t err = cudaLaunchKernelEx(&cfg, kernel, ms0, ms1, kp);
-    if (err != cudaSuccess) return fail_cuda("mxfp8_gemm_kernel launch", err);
-    MOK_LAUNCH_CHECK("mxfp8_gemm_kernel");
-    return MOK_OK;
+    static int resident_pairs[16] = {0};
+    return launch_pairs(mxfp8_gemm_kernel<MODE>, "mxfp8_gemm_kernel", resident_pairs, smem_bytes(kp.num_experts), max_tiles,
+                        stream, ms0, ms1, kp);
 }
 
-int check_problem(const GemmProblem& pb) {
-    if (pb.num_experts < 1 || pb.num_experts > MOK_MAX_LOCAL_EXPERTS) return MOK_ERR_TOO_LARGE;
-    if (pb.row_begin < 0 || pb.row_end < pb.row_begin || (pb.row_begin % BM) != 0 || (pb.row_end % BM) != 0)
-        return MOK_ERR_INVALID_ARGUMENT;
-    if (pb.tokens_per_expert == nullptr && (pb.num_experts != 1 || pb.dense_rows % BM != 0)) return MOK_ERR_INVALID_ARGUMENT;
-    if (pb.tokens_per_expert != nullptr && pb.num_tokens == nullptr) return MOK_ERR_INVALID_ARGUMENT;
-    return MOK_OK;
-}
-
-KernelParams base_params(const GemmProblem& pb) {
-    KernelParams kp{};
-    kp.tokens_per_expert = pb.tokens_per_expert;
-    kp.num_tokens = pb.num_tokens;
-    kp.num_experts = pb.num_experts;
-    kp.dense_rows = pb.dense_rows;
-    kp.row_begin = pb.row_begin;
-    kp.row_end = pb.row_end;
-    kp.n_sets = 1;
-    kp.k_sets = 1;
-    kp.status = pb.status;
-    return kp;
-}
 
 }  // namespace
 
