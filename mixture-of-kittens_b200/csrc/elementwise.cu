@@ -153,6 +153,39 @@ __global__ void __launch_bounds__(256) zero_empty_kernel(const int* __restrict__
     }
 }
 
+// One block per expert: occupied[e] = 1 + the last row (relative to the expert's first row) that carries a token, 0 if
+// none.  Padding rows (peer_rank < 0) normally sit at the tail of an expert's range; scanning the whole range keeps the
+// answer right for any placement.
+__global__ void occupied_rows_kernel(const int32_t* __restrict__ peer_rank, const int32_t* __restrict__ tokens_per_expert,
+                                     const int32_t* __restrict__ num_tokens, int schedule_capacity, int32_t* __restrict__ occupied) {
+    __shared__ int partial[8];
+    const int e = blockIdx.x;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    int before = 0;
+    for (int i = threadIdx.x; i < e; i += blockDim.x) before += tokens_per_expert[i];
+    before = __reduce_add_sync(0xffffffffu, before);
+    if (lane == 0) partial[warp] = before;
+    __syncthreads();
+    int first = 0;
+    for (int w = 0; w < 8; ++w) first += partial[w];
+    __syncthreads();
+    int limit = *num_tokens;
+    if (limit > schedule_capacity) limit = schedule_capacity;
+    int end = first + tokens_per_expert[e];
+    if (end > limit) end = limit;
+    int last = 0;
+    for (int r = first + threadIdx.x; r < end; r += blockDim.x)
+        if (peer_rank[r] >= 0) last = r - first + 1;
+    last = __reduce_max_sync(0xffffffffu, last);
+    if (lane == 0) partial[warp] = last;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int m = 0;
+        for (int w = 0; w < 8; ++w) m = max(m, partial[w]);
+        occupied[e] = m;
+    }
+}
+
 int stream_grid(long long items, int threads) {
     long long blocks = (items + threads - 1) / threads;
     const long long cap = static_cast<long long>(sm_count()) * 16;
@@ -196,6 +229,14 @@ int launch_swiglu_bwd(const void* gate, const void* up, const void* d_hidden, vo
         swiglu_bwd_kernel<false><<<grid, 256, 0, stream>>>(g, u, dh, dg, du, num_tokens, dense_rows, row_begin, row_end, vec,
                                                           limit, row_weight, row_grad);
     MOK_LAUNCH_CHECK("swiglu_bwd_kernel");
+    return MOK_OK;
+}
+
+int launch_occupied_rows(const int32_t* peer_rank, const int32_t* tokens_per_expert, const int32_t* num_tokens,
+                         int schedule_capacity, int num_experts, int32_t* occupied, cudaStream_t stream) {
+    if (!peer_rank || !tokens_per_expert || !num_tokens || !occupied || num_experts < 1) return MOK_ERR_INVALID_ARGUMENT;
+    occupied_rows_kernel<<<num_experts, 256, 0, stream>>>(peer_rank, tokens_per_expert, num_tokens, schedule_capacity, occupied);
+    MOK_LAUNCH_CHECK("occupied_rows_kernel");
     return MOK_OK;
 }
 

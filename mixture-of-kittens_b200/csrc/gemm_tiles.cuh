@@ -20,6 +20,8 @@ constexpr int MODE_WGRAD = 1;  // D[e] = sum over the rows of expert e
 struct KernelParams {
     const int32_t* tokens_per_expert;
     const int32_t* num_tokens;
+    const int32_t* occupied_rows;   // wgrad: see GemmProblem
+    int scale_slots;                // MXFP8: tensor-memory slots the scale columns rotate through
     int num_experts;
     int dense_rows;
     int row_begin, row_end;
@@ -80,7 +82,9 @@ __device__ __forceinline__ bool decode_tile(const KernelParams& p, const int* cu
         tile.n0 = (rem - mi * p.n_blocks) * BN;
         tile.set = 0;
         const int ks = max(cum[e], lo);
-        const int ke = min(cum[e + 1], hi);
+        int ke = min(cum[e + 1], hi);
+        // at least one K step, so that an expert whose range holds padding only still gets its (zero) gradient written
+        if (p.occupied_rows != nullptr) ke = min(ke, cum[e] + (max(p.occupied_rows[e], 1) + BK - 1) / BK * BK);
         tile.row0 = ks;
         tile.k_blocks = ke > ks ? (ke - ks) / BK : 0;
         tile.accumulate = cum[e] < lo ? 1 : 0;
@@ -184,6 +188,8 @@ inline KernelParams base_params(const GemmProblem& pb) {
     KernelParams kp{};
     kp.tokens_per_expert = pb.tokens_per_expert;
     kp.num_tokens = pb.num_tokens;
+    kp.occupied_rows = pb.occupied_rows;
+    kp.scale_slots = 1;
     kp.num_experts = pb.num_experts;
     kp.dense_rows = pb.dense_rows;
     kp.row_begin = pb.row_begin;

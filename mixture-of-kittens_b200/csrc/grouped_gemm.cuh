@@ -16,6 +16,9 @@ struct GemmProblem {
     int dense_rows = 0;
     int row_begin = 0, row_end = 0;
     int buffer_rows = 0;   // rows of the activation buffers (macrobatch size, or T for a dense problem)
+    // optional, weight-gradient form only: rows of each expert that can be non-zero (the rest of its 256-aligned range
+    // is zero padding); the K loop of expert e ends at this count rounded up to the K step
+    const int32_t* occupied_rows = nullptr;
     uint32_t* status = nullptr;
 };
 

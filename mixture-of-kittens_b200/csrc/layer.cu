@@ -194,6 +194,21 @@ GemmProblem routed_problem(const mok_layer_args* a, const Span& s) {
     return p;
 }
 
+// int32 [num_local_experts] behind the two per-row fp32 arrays of row_scratch
+int32_t* occupied_rows_of(const mok_layer_args* a) {
+    return reinterpret_cast<int32_t*>(a->row_scratch + 2 * static_cast<size_t>(a->macrobatch_size));
+}
+
+// MOK_NO_WGRAD_TRIM=1 lets the weight-gradient GEMMs run over the padding rows too (for measurements; same results)
+bool wgrad_trim_enabled() {
+    static int v = -1;
+    if (v < 0) {
+        const char* e = getenv("MOK_NO_WGRAD_TRIM");
+        v = (e != nullptr && e[0] == '1') ? 0 : 1;
+    }
+    return v == 1;
+}
+
 GemmProblem shared_problem(const mok_layer_args* a) {
     GemmProblem p;
     p.num_experts = 1;
@@ -475,6 +490,9 @@ extern "C" int mok_moe_backward_bf16(const mok_layer_args* a, mok_stream_t strea
 
     float* row_weight = a->row_scratch;
     float* row_grad = a->row_scratch + a->macrobatch_size;
+    int32_t* occupied = occupied_rows_of(a);
+    MOK_TRY(launch_occupied_rows(a->peer_rank, a->tokens_per_expert, a->num_tokens, a->schedule_capacity, a->num_local_experts,
+                                 occupied, s));
     for (int wi = 0; wi < num_windows(a); ++wi) {
         const Span win = window_span(a, wi);
         if (wi > 0) {   // the saved context only covers window 0: rebuild x_routed, gate, up, hidden of this window
@@ -503,7 +521,8 @@ extern "C" int mok_moe_backward_bf16(const mok_layer_args* a, mok_stream_t strea
                                       rows_bf16(a->d_x_routed, c, H), at_row(row_grad, c, 1), ctas, st);
             }));
         // weight gradients over the whole window (fixed K order = schedule order), while the last pushes drain
-        const GemmProblem p = routed_problem(a, win);
+        GemmProblem p = routed_problem(a, win);
+        if (wgrad_trim_enabled()) p.occupied_rows = occupied;
         const int tw = trace_begin("wgrad", wi, false, s);
         MOK_TRY(launch_wgrad_gemm(p, a->d_y_routed, H, a->hidden_routed, I, a->d_w_routed_down, s));
         MOK_TRY(launch_wgrad_gemm(p, a->d_gate_routed, I, a->x_routed, H, a->d_w_routed_gate, s));
@@ -614,6 +633,9 @@ extern "C" int mok_moe_backward_mxfp8(const mok_layer_args* a, mok_stream_t stre
     float* row_weight = a->row_scratch;
     float* row_grad = a->row_scratch + a->macrobatch_size;
     const long long sc_I = scale_tile_row_bytes(I);
+    int32_t* occupied = occupied_rows_of(a);
+    MOK_TRY(launch_occupied_rows(a->peer_rank, a->tokens_per_expert, a->num_tokens, a->schedule_capacity, a->num_local_experts,
+                                 occupied, s));
     for (int wi = 0; wi < num_windows(a); ++wi) {
         const Span win = window_span(a, wi);
         if (wi > 0) {
@@ -653,7 +675,8 @@ extern "C" int mok_moe_backward_mxfp8(const mok_layer_args* a, mok_stream_t stre
                 return launch_combine(a->d_x_routed_ptrs, a->d_router_weight_ptrs, a->ep_size, rows_of(a, c), a->topk, T, H,
                                       rows_bf16(a->d_x_routed, c, H), at_row(row_grad, c, 1), ctas, st);
             }));
-        const GemmProblem p = routed_problem(a, win);
+        GemmProblem p = routed_problem(a, win);
+        if (wgrad_trim_enabled()) p.occupied_rows = occupied;
         MOK_TRY(launch_fp8_wgrad_gemm(p, act_transposed(a, a->d_y_fp8_t, a->d_y_sc_t, H), H,
                                       act_transposed(a, a->hidden_fp8_t, a->hidden_sc_t, I), I, a->d_w_routed_down, s));
         MOK_TRY(launch_fp8_wgrad_gemm(p, act_transposed(a, a->d_gate_fp8_t, a->d_gate_sc_t, I), I,

@@ -5,7 +5,8 @@
 // leader CTA issues the MMAs.  In addition every K step carries its e8m0 scales: one 512-byte tile for the CTA's
 // 128 rows of A and two for the 256 columns of B (both CTAs need all B scales), loaded by TMA next to the data,
 // copied to tensor memory with tcgen05.cp and consumed by four K = 32 MMAs whose descriptor selects the scale byte.
-// Tensor memory: 256 accumulator columns + 12 scale columns, so the accumulator is single-buffered.
+// Tensor memory: 256 accumulator columns + one 12-column scale slot per pipeline stage (16 columns apart), so the
+// accumulator is single-buffered.
 // Both operands are K-major; the dgrad and wgrad forms use transposed-quantized copies of weights / activations
 // (the role MXFP8 plays in the reference grouped GEMM, csrc/megakernel/grouped_gemm.cuh:222-249).
 #include "gemm_tiles.cuh"
@@ -26,6 +27,7 @@ constexpr int SCALE_STAGE_BYTES = 3 * SCALE_TILE_BYTES;   // A rows of this CTA,
 constexpr int STAGE_TX_BYTES = DATA_STAGE_BYTES + SCALE_STAGE_BYTES;
 constexpr int TMEM_SFA_COL = 256;                     // 4 columns
 constexpr int TMEM_SFB_COL = 260;                     // 8 columns
+constexpr int SCALE_SLOT_COLS = 16;                   // columns from one scale slot to the next (slots: up to STAGES)
 
 
 struct SharedLayout {
@@ -162,15 +164,19 @@ mxfp8_gemm_kernel(const __grid_constant__ MapSet ms0, const __grid_constant__ Ma
                         const uint32_t a_addr = smem_base + stage * DATA_STAGE_BYTES;
                         const uint32_t b_addr = a_addr + A_TILE_BYTES;
                         const uint32_t s_addr = scale_base + stage * SCALE_STAGE_BYTES;
-                        tmem_copy_scales_pair(sfa_tmem, umma_scale_desc(s_addr));
-                        tmem_copy_scales_pair(sfb_tmem, umma_scale_desc(s_addr + SCALE_TILE_BYTES));
-                        tmem_copy_scales_pair(sfb_tmem + 4, umma_scale_desc(s_addr + 2 * SCALE_TILE_BYTES));
+                        // the scale columns rotate with the stage, so that the copy for this K step does not have to
+                        // wait for the MMAs of the previous one to finish reading theirs
+                        const uint32_t slot = static_cast<uint32_t>(stage % p.scale_slots) * SCALE_SLOT_COLS;
+                        const uint32_t sfa = sfa_tmem + slot, sfb = sfb_tmem + slot;
+                        tmem_copy_scales_pair(sfa, umma_scale_desc(s_addr));
+                        tmem_copy_scales_pair(sfb, umma_scale_desc(s_addr + SCALE_TILE_BYTES));
+                        tmem_copy_scales_pair(sfb + 4, umma_scale_desc(s_addr + 2 * SCALE_TILE_BYTES));
                         const uint64_t a_desc = umma_smem_desc(a_addr, 16, 1024);
                         const uint64_t b_desc = umma_smem_desc(b_addr, 16, 1024);
 #pragma unroll
                         for (int k = 0; k < BK / 32; ++k)   // 32 elements = 32 bytes = 2 descriptor units per slice
-                            umma_mxfp8_pair(tmem_base, a_desc + k * 2u, b_desc + k * 2u, umma_idesc_mxfp8(BM, BN, k), sfa_tmem,
-                                            sfb_tmem, (kb | k) != 0 ? 1u : 0u);
+                            umma_mxfp8_pair(tmem_base, a_desc + k * 2u, b_desc + k * 2u, umma_idesc_mxfp8(BM, BN, k), sfa, sfb,
+                                            (kb | k) != 0 ? 1u : 0u);
                         umma_commit_pair(bar_empty + 8 * stage);
                         if (kb == tile.k_blocks - 1) umma_commit_pair(bar_tmem_full);
                     }
@@ -287,9 +293,24 @@ int fill_set(MapSet* ms, const Fp8Operand& a, long long a_groups, const Fp8Opera
 }
 
 size_t smem_bytes(int num_experts) { return 1024 + SharedLayout::kCum + 4 * (static_cast<size_t>(num_experts) + 2); }
+// Scale slots in tensor memory: one per pipeline stage; MOK_SCALE_SLOTS (1..STAGES) overrides, for measurements.
+int scale_slots() {
+    static int slots = 0;
+    if (slots == 0) {
+        int n = STAGES;
+        if (const char* v = getenv("MOK_SCALE_SLOTS")) {
+            const int want = atoi(v);
+            if (want >= 1 && want <= STAGES) n = want;
+        }
+        slots = n;
+    }
+    return slots;
+}
+
 template <int MODE>
-int launch(const MapSet& ms0, const MapSet& ms1, const KernelParams& kp, int max_tiles, cudaStream_t stream) {
+int launch(const MapSet& ms0, const MapSet& ms1, KernelParams kp, int max_tiles, cudaStream_t stream) {
     static int resident_pairs[16] = {0};
+    kp.scale_slots = scale_slots();
     return launch_pairs(mxfp8_gemm_kernel<MODE>, "mxfp8_gemm_kernel", resident_pairs, smem_bytes(kp.num_experts), max_tiles,
                         stream, ms0, ms1, kp);
 }

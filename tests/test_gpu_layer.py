@@ -75,6 +75,36 @@ def test_layer_fwd_bwd_matches_oracle(dist_ctx, case):
     _compare(ref, out, grads, name)
 
 
+def test_cpu_plumbing_configuration_against_fp32_math(dist_ctx):
+    """The small configuration of the acceptance list (2048 tokens, hidden 512, 8 experts of intermediate 1024, top-2,
+    weights ~ N(0, 0.02), seed 0) against plain fp32 math of the same layer: rel-L2 <= 1e-2 for outputs and gradients."""
+    import mok
+    E, H, I, K, T = 8, 512, 1024, 2, 2048
+    inp = O.make_rank_inputs(0, E, E, K, T, H, I, seed=0, weight_std=0.02)
+    ref = O.moe_layer_oracle([inp], round_bf16=False)[0]
+    out, grads = _run(dist_ctx, inp, E, mok.functional.MoKConfig())
+    for name, got in (("output", out),) + tuple(zip(FIELDS, grads)):
+        _, _, l2, _ = O.error_stats(getattr(ref, name).float(), got.float().cpu())
+        assert l2 <= 1e-2, (name, l2)
+
+
+@pytest.mark.parametrize("minibatch", [256, 512, 1024, 2048])
+def test_imbalanced_routing_minibatch_sweep(dist_ctx, minibatch):
+    """Mixtral-like proportions (8 experts, intermediate 3.5x hidden, top-2) with a Zipf(1.2) expert bias, so one expert
+    takes the bulk of the routes, at schedule_capacity_multiplier 1.0 and every minibatch size of the sweep; the
+    macrobatch equals the minibatch, so the ring and the backward replay are exercised on a skewed schedule."""
+    import mok
+    E, H, I, K, T = 8, 512, 1792, 2, 2048
+    bias = 4.0 * torch.log(torch.arange(1, E + 1, dtype=torch.float32) ** -1.2)
+    inp = O.make_rank_inputs(0, E, E, K, T, H, I, seed=3, weight_std=0.02, expert_bias=bias)
+    counts = torch.bincount(inp.topk_experts.flatten(), minlength=E).float()
+    assert counts.max() / counts.sum() > 0.35                      # the skew is real
+    ref = O.moe_layer_oracle([inp])[0]
+    config = mok.functional.MoKConfig(minibatch_size=minibatch, macrobatch_size=minibatch, schedule_capacity_multiplier=1.0)
+    out, grads = _run(dist_ctx, inp, E, config)
+    _compare(ref, out, grads, f"imbalanced/minibatch={minibatch}")
+
+
 def test_layer_with_recomputed_context_and_bitwise_repeat(dist_ctx):
     import mok
     E, H, I, K, T = 8, 256, 512, 2, 1024
