@@ -204,8 +204,9 @@ typedef struct mok_layer_args {
     void *d_y_routed;      /* [MB, H] */
     void *d_w_shared_gate, *d_w_shared_up, *d_w_shared_down;
     void *d_w_routed_gate, *d_w_routed_up, *d_w_routed_down;
-    float* row_scratch;    /* 4-byte words [2 * MB + num_local_experts] (backward): fp32 router weight and router-weight
-                              gradient of every row, then int32 occupied rows of every expert */
+    float* row_scratch;    /* 4-byte words (backward): fp32 router weight [MB] and router-weight gradient [MB] of every
+                              row, int32 occupied rows of every expert [num_local_experts], and for the MXFP8 backward
+                              fp32 partial sums [MB * intermediate / 128] */
     uint32_t* status;      /* uint32 [1] */
     /* MXFP8 entry points only (NULL otherwise).  "fp8" = e4m3 bytes, "sc" = e8m0 scale tiles [rows/128, cols/128, 32, 16]
      * of the matrix as stored (scales along its last dimension).  In the MXFP8 calls the bf16 routed activation

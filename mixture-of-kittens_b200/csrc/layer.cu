@@ -199,14 +199,22 @@ int32_t* occupied_rows_of(const mok_layer_args* a) {
     return reinterpret_cast<int32_t*>(a->row_scratch + 2 * static_cast<size_t>(a->macrobatch_size));
 }
 
+// MXFP8 backward: fp32 [MB, intermediate / 128] partial sums of the router-weight gradient, behind `occupied`
+float* row_partials_of(const mok_layer_args* a) {
+    return a->row_scratch + 2 * static_cast<size_t>(a->macrobatch_size) + a->num_local_experts;
+}
+
+// MOK_NO_FUSED_ACT=1 runs the MXFP8 activation steps as separate quantize / SwiGLU / dequantize kernels (same e4m3
+// bytes; the router-weight gradient differs by summation order only)
+bool fused_activations_enabled() {
+    const char* v = getenv("MOK_NO_FUSED_ACT");
+    return !(v != nullptr && v[0] == '1');
+}
+
 // MOK_NO_WGRAD_TRIM=1 lets the weight-gradient GEMMs run over the padding rows too (for measurements; same results)
 bool wgrad_trim_enabled() {
-    static int v = -1;
-    if (v < 0) {
-        const char* e = getenv("MOK_NO_WGRAD_TRIM");
-        v = (e != nullptr && e[0] == '1') ? 0 : 1;
-    }
-    return v == 1;
+    const char* v = getenv("MOK_NO_WGRAD_TRIM");
+    return !(v != nullptr && v[0] == '1');
 }
 
 GemmProblem shared_problem(const mok_layer_args* a) {
@@ -332,6 +340,18 @@ int gate_up_hidden_mxfp8(const mok_layer_args* a, const Span& s, cudaStream_t st
     const Fp8Operand wu = weight_operand(a, a->w_up_fp8, a->w_up_sc, I, H);
     MOK_TRY(launch_fp8_rows_gemm(routed_problem(a, s), act_rows(a, a->x_fp8, a->x_sc, H, s), H, wg, &wu,
                                  rows_bf16(a->gate_routed, s, I), rows_bf16(a->up_routed, s, I), I, st));
+    if (fused_activations_enabled()) {   // one pass: e4m3 gate, up, and hidden in both layouts
+        const long long off = s.begin - s.base;
+        const long long sc_I = scale_tile_row_bytes(I);
+        auto q_at = [&](void* q) { return static_cast<uint8_t*>(q) + off * I; };
+        auto sc_at = [&](void* sc) { return static_cast<uint8_t*>(sc) + (off / 128) * sc_I; };
+        return launch_swiglu_quantize_fwd(rows_bf16(a->gate_routed, s, I), rows_bf16(a->up_routed, s, I), I, a->num_tokens, s.begin,
+                                          s.end, q_at(a->gate_fp8), sc_at(a->gate_sc), q_at(a->up_fp8), sc_at(a->up_sc),
+                                          q_at(a->hidden_fp8), sc_at(a->hidden_sc), sc_I,
+                                          static_cast<uint8_t*>(a->hidden_fp8_t) + off, a->macrobatch_size,
+                                          static_cast<uint8_t*>(a->hidden_sc_t) + (off / 128) * 512,
+                                          scale_tile_row_bytes(a->macrobatch_size), a->has_swiglu_limit != 0, a->swiglu_limit, st);
+    }
     MOK_TRY(quantize_span(a, s, a->gate_routed, I, a->gate_fp8, a->gate_sc, nullptr, nullptr, st));
     MOK_TRY(quantize_span(a, s, a->up_routed, I, a->up_fp8, a->up_sc, nullptr, nullptr, st));
     MOK_TRY(launch_swiglu_fwd(rows_bf16(a->gate_routed, s, I), rows_bf16(a->up_routed, s, I), rows_bf16(a->hidden_routed, s, I),
@@ -654,6 +674,23 @@ extern "C" int mok_moe_backward_mxfp8(const mok_layer_args* a, mok_stream_t stre
                 MOK_TRY(quantize_span(a, c, a->d_y_routed, H, a->d_y_fp8, a->d_y_sc, a->d_y_fp8_t, a->d_y_sc_t, st));
                 MOK_TRY(launch_fp8_rows_gemm(p, act_rows(a, a->d_y_fp8, a->d_y_sc, H, c), H, wd_t, nullptr,
                                              rows_bf16(a->d_hidden_routed, c, I), nullptr, I, st));
+                if (fused_activations_enabled()) {   // saved e4m3 gate / up + d_hidden -> e4m3 d_gate, d_up in one pass
+                    auto q_at = [&](void* q) { return static_cast<uint8_t*>(q) + off * I; };
+                    auto sc_at = [&](void* sc) { return static_cast<uint8_t*>(sc) + (off / 128) * sc_I; };
+                    auto qt_at = [&](void* q) { return static_cast<uint8_t*>(q) + off; };
+                    auto sct_at = [&](void* sc) { return static_cast<uint8_t*>(sc) + (off / 128) * 512; };
+                    float* partial = row_partials_of(a) + off * (I / 128);
+                    MOK_TRY(launch_swiglu_quantize_bwd(
+                        q_at(a->gate_fp8), sc_at(a->gate_sc), q_at(a->up_fp8), sc_at(a->up_sc), rows_bf16(a->d_hidden_routed, c, I), I,
+                        a->num_tokens, c.begin, c.end, q_at(a->d_gate_fp8), sc_at(a->d_gate_sc), q_at(a->d_up_fp8), sc_at(a->d_up_sc),
+                        sc_I, qt_at(a->d_gate_fp8_t), sct_at(a->d_gate_sc_t), qt_at(a->d_up_fp8_t), sct_at(a->d_up_sc_t),
+                        a->macrobatch_size, scale_tile_row_bytes(a->macrobatch_size), partial, clamp, a->swiglu_limit, st));
+                    MOK_TRY(launch_router_grad(partial, I / 128, at_row(row_weight, c, 1), at_row(row_grad, c, 1), a->num_tokens,
+                                               c.begin, c.end, st));
+                    return launch_fp8_rows_gemm_dual(p, act_rows(a, a->d_gate_fp8, a->d_gate_sc, I, c),
+                                                     act_rows(a, a->d_up_fp8, a->d_up_sc, I, c), I, wg_t, wu_t,
+                                                     rows_bf16(a->d_x_routed, c, H), H, st);
+                }
                 // the saved gate / up are e4m3: expand them (exactly) into the bf16 scratch the SwiGLU backward reads
                 MOK_TRY(launch_dequantize_rows(static_cast<const uint8_t*>(a->gate_fp8) + off * I,
                                                static_cast<const uint8_t*>(a->gate_sc) + (off / 128) * sc_I, sc_I,

@@ -11,6 +11,7 @@
 // activation buffer, limited on the device by the padded token count; the transposed output then is a column range
 // of a wider [cols, buffer_rows] matrix).
 #include "mxfp8.cuh"
+#include "swiglu_math.cuh"
 
 namespace mok {
 namespace {
@@ -31,6 +32,33 @@ __device__ __forceinline__ void store_staged_rows(const uint8_t* otile, uint8_t*
         *reinterpret_cast<uint4*>(out + static_cast<long long>(r) * ld + seg * 16) =
             *reinterpret_cast<const uint4*>(otile + r * kOutPitch + seg * 16);
     }
+}
+
+// Transposed layout of a staged bf16 tile: thread = column of the tile = row of the transpose, four blocks of 32 down
+// the column.  `out` is the transposed tile's first byte (rows `ld` apart), `scale_tile` its 512-byte scale tile.
+// Every thread of the block calls; the tile must be complete (a barrier before the call is the caller's).
+__device__ __forceinline__ void quantize_tile_transposed(const uint8_t* tile, uint8_t* otile, int tid, uint8_t* out, long long ld,
+                                                         uint8_t* scale_tile) {
+    uint32_t scale_word = 0;
+    uint8_t* mine = otile + tid * kOutPitch;
+#pragma unroll
+    for (int kb = 0; kb < 4; ++kb) {
+        uint32_t packed[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+            const uint16_t lo = *reinterpret_cast<const uint16_t*>(tile + (kb * 32 + 2 * i) * kRowPitch + tid * 2);
+            const uint16_t hi = *reinterpret_cast<const uint16_t*>(tile + (kb * 32 + 2 * i + 1) * kRowPitch + tid * 2);
+            packed[i] = static_cast<uint32_t>(lo) | (static_cast<uint32_t>(hi) << 16);
+        }
+        uint32_t out8[8], sbyte;
+        mxfp8_quantize_block(packed, out8, sbyte);
+        scale_word |= sbyte << (kb * 8);
+        *reinterpret_cast<uint4*>(mine + kb * 32) = make_uint4(out8[0], out8[1], out8[2], out8[3]);
+        *reinterpret_cast<uint4*>(mine + kb * 32 + 16) = make_uint4(out8[4], out8[5], out8[6], out8[7]);
+    }
+    __syncthreads();
+    store_staged_rows(otile, out, ld, tid);
+    *reinterpret_cast<uint32_t*>(scale_tile + (tid & 31) * 16 + (tid >> 5) * 4) = scale_word;
 }
 
 struct QuantArgs {
@@ -91,29 +119,139 @@ __global__ void __launch_bounds__(128) quantize_kernel(const QuantArgs a) {
         uint8_t* sdst = a.sc + e * a.sc_mat_stride + tr * a.sc_row_tile_stride + static_cast<long long>(tc) * 512;
         *reinterpret_cast<uint32_t*>(sdst + (tid & 31) * 16 + (tid >> 5) * 4) = scale_word;
     }
-    if (a.qt != nullptr) {  // thread = column of the tile = row of the transpose, four blocks of 32 down the column
-        uint32_t scale_word = 0;
-        uint8_t* out = a.qt + e * a.qt_mat_stride + static_cast<long long>(tc) * kTile * a.qt_ld + static_cast<long long>(tr) * kTile;
-        uint8_t* mine = otile + tid * kOutPitch;
+    if (a.qt != nullptr)
+        quantize_tile_transposed(tile, otile, tid,
+                                 a.qt + e * a.qt_mat_stride + static_cast<long long>(tc) * kTile * a.qt_ld + static_cast<long long>(tr) * kTile,
+                                 a.qt_ld, a.sct + e * a.sct_mat_stride + tc * a.sct_row_tile_stride + static_cast<long long>(tr) * 512);
+}
+
+// ---- fused activation steps ---------------------------------------------------------------------------------------
+// Both kernels walk a 128 x 128 tile with 16 lanes per row and eight consecutive columns per lane, sixteen rows per
+// thread: a block of 32 along the row is four adjacent lanes, so the normal layout is quantized straight from
+// registers (mxfp8_quantize_quarter) and stored as full 128-byte lines; the values that also need the transposed
+// layout go through the shared-memory tile.
+struct FusedFwdArgs {
+    const bf16 *gate, *up;
+    uint8_t *gate_q, *gate_sc, *up_q, *up_sc, *hidden_q, *hidden_sc, *hidden_qt, *hidden_sct;
+    long long sc_row_tile_stride, qt_ld, sct_row_tile_stride;
+    const int* num_tokens;
+    int row_begin, row_end, cols;
+    float limit;
+};
+
+template <bool CLAMP>
+__global__ void __launch_bounds__(128) swiglu_quantize_fwd_kernel(const FusedFwdArgs a) {
+    extern __shared__ __align__(16) uint8_t quant_smem[];
+    uint8_t* tile = quant_smem;
+    uint8_t* otile = quant_smem + kTile * kRowPitch;
+    const int tid = threadIdx.x, v = tid & 15, rq = tid >> 4;
+    const int tc = blockIdx.x, tr = blockIdx.y;
+    const int limit_row = min(a.row_end, *a.num_tokens);
+    if (a.row_begin + tr * kTile >= limit_row) return;
+    const long long sc_off = tr * a.sc_row_tile_stride + static_cast<long long>(tc) * 512;
+#pragma unroll 4
+    for (int j = 0; j < 16; ++j) {
+        const int r = rq + 8 * j;
+        const long long off = (static_cast<long long>(tr) * kTile + r) * a.cols + tc * kTile + v * 8;
+        const uint4 g = *reinterpret_cast<const uint4*>(a.gate + off);
+        const uint4 u = *reinterpret_cast<const uint4*>(a.up + off);
+        uint4 h;
+        h.x = swiglu_pair<CLAMP>(g.x, u.x, a.limit);
+        h.y = swiglu_pair<CLAMP>(g.y, u.y, a.limit);
+        h.z = swiglu_pair<CLAMP>(g.z, u.z, a.limit);
+        h.w = swiglu_pair<CLAMP>(g.w, u.w, a.limit);
+        const int sidx = (r & 31) * 16 + (r >> 5) * 4 + (v >> 2);
+        uint2 q;
+        uint32_t sb;
+        mxfp8_quantize_quarter(g, q, sb);
+        *reinterpret_cast<uint2*>(a.gate_q + off) = q;
+        if ((v & 3) == 0) a.gate_sc[sc_off + sidx] = static_cast<uint8_t>(sb);
+        mxfp8_quantize_quarter(u, q, sb);
+        *reinterpret_cast<uint2*>(a.up_q + off) = q;
+        if ((v & 3) == 0) a.up_sc[sc_off + sidx] = static_cast<uint8_t>(sb);
+        mxfp8_quantize_quarter(h, q, sb);
+        *reinterpret_cast<uint2*>(a.hidden_q + off) = q;
+        if ((v & 3) == 0) a.hidden_sc[sc_off + sidx] = static_cast<uint8_t>(sb);
+        *reinterpret_cast<uint4*>(tile + r * kRowPitch + v * 16) = h;
+    }
+    __syncthreads();
+    quantize_tile_transposed(tile, otile, tid, a.hidden_qt + static_cast<long long>(tc) * kTile * a.qt_ld + static_cast<long long>(tr) * kTile,
+                             a.qt_ld, a.hidden_sct + tc * a.sct_row_tile_stride + static_cast<long long>(tr) * 512);
+}
+
+struct FusedBwdArgs {
+    const uint8_t *gate_q, *gate_sc, *up_q, *up_sc;
+    const bf16* d_hidden;
+    uint8_t *dg_q, *dg_sc, *du_q, *du_sc, *dg_qt, *dg_sct, *du_qt, *du_sct;
+    long long sc_row_tile_stride, qt_ld, sct_row_tile_stride;
+    float* row_partial;
+    const int* num_tokens;
+    int row_begin, row_end, cols;
+    float limit;
+};
+
+template <bool CLAMP>
+__global__ void __launch_bounds__(128) swiglu_quantize_bwd_kernel(const FusedBwdArgs a) {
+    extern __shared__ __align__(16) uint8_t quant_smem[];
+    uint8_t* tile = quant_smem;
+    uint8_t* otile = quant_smem + kTile * kRowPitch;
+    const int tid = threadIdx.x, v = tid & 15, rq = tid >> 4;
+    const int tc = blockIdx.x, tr = blockIdx.y;
+    const int limit_row = min(a.row_end, *a.num_tokens);
+    if (a.row_begin + tr * kTile >= limit_row) return;
+    const long long sc_off = tr * a.sc_row_tile_stride + static_cast<long long>(tc) * 512;
+    const int tiles = a.cols / kTile;
+    uint4 du_keep[16];   // d_up waits in registers while d_gate uses the shared-memory tile
 #pragma unroll
-        for (int kb = 0; kb < 4; ++kb) {
-            uint32_t packed[16];
+    for (int j = 0; j < 16; ++j) {
+        const int r = rq + 8 * j;
+        const long long row = static_cast<long long>(tr) * kTile + r;
+        const long long off = row * a.cols + tc * kTile + v * 8;
+        const uint2 gq = *reinterpret_cast<const uint2*>(a.gate_q + off);
+        const uint2 uq = *reinterpret_cast<const uint2*>(a.up_q + off);
+        const uint4 dh = *reinterpret_cast<const uint4*>(a.d_hidden + off);
+        const int sidx = (r & 31) * 16 + (r >> 5) * 4 + (v >> 2);
+        const uint4 g = mxfp8_dequantize8(gq, a.gate_sc[sc_off + sidx]);
+        const uint4 u = mxfp8_dequantize8(uq, a.up_sc[sc_off + sidx]);
+        uint4 dg, du;
+        float acc = swiglu_bwd_pair<CLAMP>(g.x, u.x, dh.x, a.limit, dg.x, du.x);
+        acc += swiglu_bwd_pair<CLAMP>(g.y, u.y, dh.y, a.limit, dg.y, du.y);
+        acc += swiglu_bwd_pair<CLAMP>(g.z, u.z, dh.z, a.limit, dg.z, du.z);
+        acc += swiglu_bwd_pair<CLAMP>(g.w, u.w, dh.w, a.limit, dg.w, du.w);
 #pragma unroll
-            for (int i = 0; i < 16; ++i) {
-                const uint16_t lo = *reinterpret_cast<const uint16_t*>(tile + (kb * 32 + 2 * i) * kRowPitch + tid * 2);
-                const uint16_t hi = *reinterpret_cast<const uint16_t*>(tile + (kb * 32 + 2 * i + 1) * kRowPitch + tid * 2);
-                packed[i] = static_cast<uint32_t>(lo) | (static_cast<uint32_t>(hi) << 16);
-            }
-            uint32_t out8[8], sbyte;
-            mxfp8_quantize_block(packed, out8, sbyte);
-            scale_word |= sbyte << (kb * 8);
-            *reinterpret_cast<uint4*>(mine + kb * 32) = make_uint4(out8[0], out8[1], out8[2], out8[3]);
-            *reinterpret_cast<uint4*>(mine + kb * 32 + 16) = make_uint4(out8[4], out8[5], out8[6], out8[7]);
-        }
-        __syncthreads();
-        store_staged_rows(otile, out, a.qt_ld, tid);
-        uint8_t* sdst = a.sct + e * a.sct_mat_stride + tc * a.sct_row_tile_stride + static_cast<long long>(tr) * 512;
-        *reinterpret_cast<uint32_t*>(sdst + (tid & 31) * 16 + (tid >> 5) * 4) = scale_word;
+        for (int off_l = 1; off_l < 16; off_l <<= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off_l);   // the row's 16 lanes
+        if (v == 0) a.row_partial[row * tiles + tc] = acc;
+        uint2 q;
+        uint32_t sb;
+        mxfp8_quantize_quarter(dg, q, sb);
+        *reinterpret_cast<uint2*>(a.dg_q + off) = q;
+        if ((v & 3) == 0) a.dg_sc[sc_off + sidx] = static_cast<uint8_t>(sb);
+        mxfp8_quantize_quarter(du, q, sb);
+        *reinterpret_cast<uint2*>(a.du_q + off) = q;
+        if ((v & 3) == 0) a.du_sc[sc_off + sidx] = static_cast<uint8_t>(sb);
+        *reinterpret_cast<uint4*>(tile + r * kRowPitch + v * 16) = dg;
+        du_keep[j] = du;
+    }
+    __syncthreads();
+    const long long t_off = static_cast<long long>(tc) * kTile * a.qt_ld + static_cast<long long>(tr) * kTile;
+    const long long ts_off = tc * a.sct_row_tile_stride + static_cast<long long>(tr) * 512;
+    quantize_tile_transposed(tile, otile, tid, a.dg_qt + t_off, a.qt_ld, a.dg_sct + ts_off);
+    __syncthreads();
+#pragma unroll
+    for (int j = 0; j < 16; ++j) *reinterpret_cast<uint4*>(tile + (rq + 8 * j) * kRowPitch + v * 16) = du_keep[j];
+    __syncthreads();
+    quantize_tile_transposed(tile, otile, tid, a.du_qt + t_off, a.qt_ld, a.du_sct + ts_off);
+}
+
+__global__ void __launch_bounds__(256) router_grad_kernel(const float* __restrict__ row_partial, int tiles,
+                                                           const float* __restrict__ row_weight, float* __restrict__ row_grad,
+                                                           const int* __restrict__ num_tokens, int row_begin, int row_end) {
+    const int rows = min(row_end, *num_tokens) - row_begin;
+    for (int row = blockIdx.x * blockDim.x + threadIdx.x; row < rows; row += gridDim.x * blockDim.x) {
+        float acc = 0.0f;
+        for (int t = 0; t < tiles; ++t) acc += row_partial[static_cast<long long>(row) * tiles + t];
+        const float w = row_weight[row];
+        row_grad[row] = w > 0.0f ? acc / w : 0.0f;
     }
 }
 
@@ -206,6 +344,119 @@ int launch_dequantize_rows(const void* q, const void* sc, long long sc_row_tile_
                                                                     sc_row_tile_stride, static_cast<bf16*>(out), cols, num_tokens,
                                                                     row_begin, row_end);
     MOK_LAUNCH_CHECK("mxfp8_dequantize_kernel");
+    return MOK_OK;
+}
+
+namespace {
+
+// Raises the dynamic shared-memory limit of one kernel instantiation once per device.
+template <typename Kernel>
+int enable_tile_smem(Kernel kernel, bool (&done)[16]) {
+    int dev = 0;
+    MOK_CUDA_CHECK(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 16) return MOK_ERR_UNSUPPORTED;
+    if (!done[dev]) {
+        MOK_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kQuantSmemBytes));
+        done[dev] = true;
+    }
+    return MOK_OK;
+}
+
+template <typename Kernel, typename Args>
+int launch_tile_kernel(Kernel kernel, const char* name, bool (&done)[16], const Args& args, int cols, int rows, cudaStream_t stream) {
+    if (rows / 128 > 65535) return MOK_ERR_TOO_LARGE;
+    if (int rc = enable_tile_smem(kernel, done)) return rc;
+    dim3 grid(cols / 128, rows / 128, 1);
+    kernel<<<grid, 128, kQuantSmemBytes, stream>>>(args);
+    MOK_LAUNCH_CHECK(name);
+    return MOK_OK;
+}
+
+}  // namespace
+
+int launch_swiglu_quantize_fwd(const void* gate, const void* up, int cols, const int32_t* num_tokens, int row_begin, int row_end,
+                               void* gate_q, void* gate_sc, void* up_q, void* up_sc, void* hidden_q, void* hidden_sc,
+                               long long sc_row_tile_stride, void* hidden_qt, long long qt_ld, void* hidden_sct,
+                               long long sct_row_tile_stride, bool has_limit, float limit, cudaStream_t stream) {
+    if (!gate || !up || !num_tokens || !gate_q || !gate_sc || !up_q || !up_sc || !hidden_q || !hidden_sc || !hidden_qt || !hidden_sct)
+        return MOK_ERR_INVALID_ARGUMENT;
+    if (cols <= 0 || cols % 128 != 0 || row_end <= row_begin || (row_end - row_begin) % 128 != 0) return MOK_ERR_INVALID_ARGUMENT;
+    FusedFwdArgs a{};
+    a.gate = static_cast<const bf16*>(gate);
+    a.up = static_cast<const bf16*>(up);
+    a.gate_q = static_cast<uint8_t*>(gate_q);
+    a.gate_sc = static_cast<uint8_t*>(gate_sc);
+    a.up_q = static_cast<uint8_t*>(up_q);
+    a.up_sc = static_cast<uint8_t*>(up_sc);
+    a.hidden_q = static_cast<uint8_t*>(hidden_q);
+    a.hidden_sc = static_cast<uint8_t*>(hidden_sc);
+    a.hidden_qt = static_cast<uint8_t*>(hidden_qt);
+    a.hidden_sct = static_cast<uint8_t*>(hidden_sct);
+    a.sc_row_tile_stride = sc_row_tile_stride;
+    a.qt_ld = qt_ld;
+    a.sct_row_tile_stride = sct_row_tile_stride;
+    a.num_tokens = num_tokens;
+    a.row_begin = row_begin;
+    a.row_end = row_end;
+    a.cols = cols;
+    a.limit = limit;
+    static bool done_clamp[16] = {false}, done_plain[16] = {false};
+    if (has_limit)
+        return launch_tile_kernel(swiglu_quantize_fwd_kernel<true>, "swiglu_quantize_fwd_kernel", done_clamp, a, cols,
+                                  row_end - row_begin, stream);
+    return launch_tile_kernel(swiglu_quantize_fwd_kernel<false>, "swiglu_quantize_fwd_kernel", done_plain, a, cols,
+                              row_end - row_begin, stream);
+}
+
+int launch_swiglu_quantize_bwd(const void* gate_q, const void* gate_sc, const void* up_q, const void* up_sc, const void* d_hidden,
+                               int cols, const int32_t* num_tokens, int row_begin, int row_end, void* d_gate_q, void* d_gate_sc,
+                               void* d_up_q, void* d_up_sc, long long sc_row_tile_stride, void* d_gate_qt, void* d_gate_sct,
+                               void* d_up_qt, void* d_up_sct, long long qt_ld, long long sct_row_tile_stride, float* row_partial,
+                               bool has_limit, float limit, cudaStream_t stream) {
+    if (!gate_q || !gate_sc || !up_q || !up_sc || !d_hidden || !num_tokens || !d_gate_q || !d_gate_sc || !d_up_q || !d_up_sc ||
+        !d_gate_qt || !d_gate_sct || !d_up_qt || !d_up_sct || !row_partial)
+        return MOK_ERR_INVALID_ARGUMENT;
+    if (cols <= 0 || cols % 128 != 0 || row_end <= row_begin || (row_end - row_begin) % 128 != 0) return MOK_ERR_INVALID_ARGUMENT;
+    FusedBwdArgs a{};
+    a.gate_q = static_cast<const uint8_t*>(gate_q);
+    a.gate_sc = static_cast<const uint8_t*>(gate_sc);
+    a.up_q = static_cast<const uint8_t*>(up_q);
+    a.up_sc = static_cast<const uint8_t*>(up_sc);
+    a.d_hidden = static_cast<const bf16*>(d_hidden);
+    a.dg_q = static_cast<uint8_t*>(d_gate_q);
+    a.dg_sc = static_cast<uint8_t*>(d_gate_sc);
+    a.du_q = static_cast<uint8_t*>(d_up_q);
+    a.du_sc = static_cast<uint8_t*>(d_up_sc);
+    a.dg_qt = static_cast<uint8_t*>(d_gate_qt);
+    a.dg_sct = static_cast<uint8_t*>(d_gate_sct);
+    a.du_qt = static_cast<uint8_t*>(d_up_qt);
+    a.du_sct = static_cast<uint8_t*>(d_up_sct);
+    a.sc_row_tile_stride = sc_row_tile_stride;
+    a.qt_ld = qt_ld;
+    a.sct_row_tile_stride = sct_row_tile_stride;
+    a.row_partial = row_partial;
+    a.num_tokens = num_tokens;
+    a.row_begin = row_begin;
+    a.row_end = row_end;
+    a.cols = cols;
+    a.limit = limit;
+    static bool done_clamp[16] = {false}, done_plain[16] = {false};
+    if (has_limit)
+        return launch_tile_kernel(swiglu_quantize_bwd_kernel<true>, "swiglu_quantize_bwd_kernel", done_clamp, a, cols,
+                                  row_end - row_begin, stream);
+    return launch_tile_kernel(swiglu_quantize_bwd_kernel<false>, "swiglu_quantize_bwd_kernel", done_plain, a, cols,
+                              row_end - row_begin, stream);
+}
+
+int launch_router_grad(const float* row_partial, int tiles, const float* row_weight, float* row_grad, const int32_t* num_tokens,
+                       int row_begin, int row_end, cudaStream_t stream) {
+    if (!row_partial || !row_weight || !row_grad || !num_tokens || tiles <= 0 || row_end <= row_begin) return MOK_ERR_INVALID_ARGUMENT;
+    long long blocks = (static_cast<long long>(row_end - row_begin) + 255) / 256;
+    const long long cap = static_cast<long long>(sm_count()) * 8;
+    if (blocks > cap) blocks = cap;
+    router_grad_kernel<<<static_cast<int>(blocks), 256, 0, stream>>>(row_partial, tiles, row_weight, row_grad, num_tokens, row_begin,
+                                                                     row_end);
+    MOK_LAUNCH_CHECK("router_grad_kernel");
     return MOK_OK;
 }
 

@@ -832,7 +832,7 @@ def dispatch_mlp_swiglu_combine_bwd_mxfp8(
     d_y_t, d_y_t_sc = _new_fp8(x, H, MB)
     d_gate_t, d_gate_t_sc = _new_fp8(x, I, MB)
     d_up_t, d_up_t_sc = _new_fp8(x, I, MB)
-    row_scratch = torch.empty(2 * MB + E, dtype=torch.float32, device=dev)
+    row_scratch = torch.empty(2 * MB + E + MB * (I // 128), dtype=torch.float32, device=dev)
 
     a = _layer_args(ep_size=ep_size, rank=_local_rank(x, x_ptrs), x=x, intermediate=I, num_local_experts=E, topk=topk,
                     capacity=cap, macrobatch_size=MB, minibatch_size=minibatch_size, num_comm_sms=num_comm_sms,

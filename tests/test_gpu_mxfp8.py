@@ -146,6 +146,27 @@ def test_mxfp8_layer_bitwise_repeat(dist_ctx):
         assert torch.equal(a, b), f"{name} is not bitwise reproducible"
 
 
+@pytest.mark.parametrize("limit", [None, 4.0])
+def test_fused_activation_kernels_equal_the_separate_ones(dist_ctx, monkeypatch, limit):
+    """The fused SwiGLU + quantize kernels (forward: e4m3 gate, up, hidden; backward: e4m3 d_gate, d_up from the saved
+    e4m3 gate / up) produce the same bytes as quantize / SwiGLU / dequantize run one after the other, so every output is
+    bitwise equal; only the router-weight gradient is summed in another order (per 128-column tile first)."""
+    import mok
+    E, H, I, K, T = 8, 256, 512, 2, 1024
+    config = mok.functional.MoKConfig(minibatch_size=256, macrobatch_size=1024)   # three windows: the ring is covered too
+    inp = O.make_rank_inputs(0, E, E, K, T, H, I)
+    monkeypatch.setenv("MOK_NO_FUSED_ACT", "1")
+    out_a, grads_a = _run_mxfp8_layer(dist_ctx, inp, E, config, limit)
+    monkeypatch.delenv("MOK_NO_FUSED_ACT")
+    out_b, grads_b = _run_mxfp8_layer(dist_ctx, inp, E, config, limit)
+    assert torch.equal(out_a, out_b)
+    for name, a, b in zip(FIELDS, grads_a, grads_b):
+        if name == "d_router_weights":
+            torch.testing.assert_close(a, b, rtol=1e-4, atol=1e-5)
+        else:
+            assert torch.equal(a, b), f"{name} differs between the fused and the separate activation kernels"
+
+
 @pytest.mark.parametrize("counts,M,N", [(None, 256, 256), ([256, 0, 768], 256, 512), ([512, 512], 512, 256)])
 def test_mxfp8_grouped_wgrad(dev, counts, M, N):
     from mok import _native as nat
