@@ -29,6 +29,8 @@ for _p in (ROOT, os.path.join(ROOT, "mixture-of-kittens_b200")):
 WORKLOADS = {
     # name: tokens/rank, hidden, experts (global), intermediate, topk, weight std, bias std
     "c2": dict(T=32768, H=7168, E=256, I=2048, K=8, std=0.006, bias=0.0, label="deepseek-v3-shaped bf16"),
+    # the benchmark's row shapes on a few GB of device memory: the case profiler captures of the bandwidth kernels use
+    "c2s": dict(T=4096, H=7168, E=16, I=2048, K=8, std=0.006, bias=0.0, label="deepseek-v3-shaped bf16, 16 experts"),
     "c1": dict(T=16384, H=2048, E=128, I=768, K=8, std=0.02, bias=0.5, label="qwen3-moe-shaped bf16"),
     "c0": dict(T=2048, H=512, E=8, I=1024, K=2, std=0.02, bias=0.0, label="cpu-plumbing shape"),
     "tiny": dict(T=512, H=256, E=8, I=256, K=2, std=0.02, bias=0.0, label="tiny"),
