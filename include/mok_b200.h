@@ -295,6 +295,28 @@ int mok_grouped_wgrad_mxfp8(const void* At_fp8, const void* At_sc, const void* B
                             const int32_t* tokens_per_expert, const int32_t* num_tokens, int num_experts, int rows,
                             int M, int N, uint32_t* status, mok_stream_t stream);
 
+/*
+ * Router in front of the layer.  No counterpart among the reference's operators: there the routes and router weights
+ * are inputs that the caller computes (README.md:128-129; its tests use torch.topk and a softmax over the selected
+ * logits, tests/utils.py:82-84).  These two entry points compute exactly those tensors, and their gradient, on the
+ * device.
+ *
+ * forward:  logits [T, padded_experts] fp32 (scratch / output) = x [T, H] bf16 * (w_hi + w_lo)^T, with the weight
+ *           given as one or two bf16 terms [padded_experts, H] (w_lo may be NULL; rows >= num_experts must be zero);
+ *           top_experts int32 [T, topk] = indices of the topk largest of logits[:, :num_experts] + bias, descending,
+ *           ties towards the lower index; router_weights fp32 [T, topk] = softmax over those topk values.
+ *           T % 256 == 0, H % 64 == 0, padded_experts % 256 == 0, num_experts <= 1024, topk <= 32.
+ * backward: d_logits bf16 [T, padded_experts] (scratch / output) = softmax backward of d_router_weights scattered to
+ *           the selected columns; d_w fp32 [padded_experts, H] = d_logits^T x; d_x bf16 [T, H] = d_logits * w_hi;
+ *           d_bias fp32 [num_experts] (may be NULL) = column sums of d_logits.  H % 256 == 0.
+ */
+int mok_router_forward(const void* x, const void* w_hi, const void* w_lo, const float* bias, int64_t num_tokens, int hidden,
+                       int num_experts, int padded_experts, int topk, float* logits, int32_t* top_experts,
+                       float* router_weights, uint32_t* status, mok_stream_t stream);
+int mok_router_backward(const void* x, const void* w_hi, const int32_t* top_experts, const float* router_weights,
+                        const float* d_router_weights, int64_t num_tokens, int hidden, int num_experts, int padded_experts,
+                        int topk, void* d_logits, void* d_x, float* d_w, float* d_bias, uint32_t* status, mok_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

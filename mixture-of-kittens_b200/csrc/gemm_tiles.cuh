@@ -33,6 +33,7 @@ struct KernelParams {
     int n_tiles_per_expert;   // MXFP8 rows form: N / 128, scale row tiles of one expert's weight
     bf16* D0;
     bf16* D1;
+    int out_f32;              // bf16 kernel: D0 is an fp32 array (router logits and router weight gradient)
     long long ldd;
     long long d_expert_stride;
     uint32_t* status;
@@ -140,6 +141,13 @@ __device__ __forceinline__ void store_row_chunk(bf16* dst, const uint32_t (&acc)
         w.w = pack_bf16x2(f[6], f[7]);
         out[v] = w;
     }
+}
+
+// 32 fp32 columns of this thread's row, stored as they are (one 128-byte line per thread).
+__device__ __forceinline__ void store_row_chunk_f32(float* dst, const uint32_t (&acc)[32]) {
+    uint4* out = reinterpret_cast<uint4*>(dst);
+#pragma unroll
+    for (int v = 0; v < 8; ++v) out[v] = make_uint4(acc[v * 4], acc[v * 4 + 1], acc[v * 4 + 2], acc[v * 4 + 3]);
 }
 
 // ---------------------------------------------------------------------------------------------------------

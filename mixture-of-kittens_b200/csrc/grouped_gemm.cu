@@ -221,7 +221,11 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_const
                 tmem_ld_32x32(taddr + c * 64, v0);
                 tmem_ld_32x32(taddr + c * 64 + 32, v1);
                 tmem_ld_wait();
-                if (tile.accumulate) {   // rare (later windows of a multi-window backward): add in fp32 per row
+                if (p.out_f32) {         // router GEMMs: the accumulator goes out unrounded (`out` was computed for 2-byte elements)
+                    float* out32 = reinterpret_cast<float*>(p.D0) + (out - p.D0) + c * 64;
+                    store_row_chunk_f32(out32, v0);
+                    store_row_chunk_f32(out32 + 32, v1);
+                } else if (tile.accumulate) {   // rare (later windows of a multi-window backward): add in fp32 per row
                     store_row_chunk(out + c * 64, v0, true);
                     store_row_chunk(out + c * 64 + 32, v1, true);
                 } else {
@@ -324,7 +328,29 @@ int launch_rows_gemm_dual(const GemmProblem& pb, const void* A0, const void* A1,
     return launch<MODE_ROWS, true>(a0, b0, a1, b1, kp, (window / BM) * kp.n_blocks, stream);
 }
 
-int launch_wgrad_gemm(const GemmProblem& pb, const void* A, int M, const void* B, int N, void* D, cudaStream_t stream) {
+int launch_rows_gemm_f32(const GemmProblem& pb, const void* A, int K, const void* B_hi, const void* B_lo, float* D, int N,
+                         cudaStream_t stream) {
+    int rc = check_problem(pb);
+    if (rc != MOK_OK) return rc;
+    if (K <= 0 || N <= 0 || K % BK != 0 || N % BN != 0 || D == nullptr) return MOK_ERR_INVALID_ARGUMENT;
+    CUtensorMap a0, b0, b1;
+    if ((rc = make_map(&a0, A, K, pb.buffer_rows, 1, BK, BM_CTA)) != MOK_OK) return rc;
+    if ((rc = make_map(&b0, B_hi, K, N, pb.num_experts, BK, BN_CTA)) != MOK_OK) return rc;
+    if ((rc = make_map(&b1, B_lo ? B_lo : B_hi, K, N, pb.num_experts, BK, BN_CTA)) != MOK_OK) return rc;
+    KernelParams kp = base_params(pb);
+    kp.n_blocks = N / BN;
+    kp.k_blocks = K / BK;
+    kp.k_sets = B_lo ? 2 : 1;      // second K loop: the same A against the low-order term
+    kp.D0 = reinterpret_cast<bf16*>(D);
+    kp.D1 = nullptr;
+    kp.out_f32 = 1;
+    kp.ldd = N;
+    const int window = pb.row_end - pb.row_begin;
+    return launch<MODE_ROWS, false>(a0, b0, a0, b1, kp, (window / BM) * kp.n_blocks, stream);
+}
+
+int launch_wgrad_gemm(const GemmProblem& pb, const void* A, int M, const void* B, int N, void* D, cudaStream_t stream,
+                      bool out_f32) {
     int rc = check_problem(pb);
     if (rc != MOK_OK) return rc;
     if (M <= 0 || N <= 0 || M % BM != 0 || N % BN != 0) return MOK_ERR_INVALID_ARGUMENT;
@@ -335,6 +361,7 @@ int launch_wgrad_gemm(const GemmProblem& pb, const void* A, int M, const void* B
     kp.n_blocks = N / BN;
     kp.m_blocks_w = M / BM;
     kp.D0 = static_cast<bf16*>(D);
+    kp.out_f32 = out_f32 ? 1 : 0;
     kp.ldd = N;
     kp.d_expert_stride = static_cast<long long>(M) * N;
     return launch<MODE_WGRAD, true>(a0, b0, a0, b0, kp, pb.num_experts * kp.m_blocks_w * kp.n_blocks, stream);

@@ -32,6 +32,13 @@ int launch_rows_gemm_dual(const GemmProblem& pb, const void* A0, const void* A1,
                           void* D, int N, cudaStream_t stream);
 
 // D[e] [M, N] (+)= A[rows_e, M]^T * B[rows_e, N]; accumulates when expert e's rows began before row_begin.
-int launch_wgrad_gemm(const GemmProblem& pb, const void* A, int M, const void* B, int N, void* D, cudaStream_t stream);
+// out_f32: D is fp32 and is overwritten (single-window problems only).
+int launch_wgrad_gemm(const GemmProblem& pb, const void* A, int M, const void* B, int N, void* D, cudaStream_t stream,
+                      bool out_f32 = false);
+
+// fp32 D[row, :] = A[row, :K] * (B_hi[e] + B_lo[e])^T with B_* stored [E, N, K]; B_lo may be nullptr.  Two bf16 terms
+// carry an fp32 weight matrix to about 16 mantissa bits, which the router logits need (fp32 accumulation throughout).
+int launch_rows_gemm_f32(const GemmProblem& pb, const void* A, int K, const void* B_hi, const void* B_lo, float* D, int N,
+                         cudaStream_t stream);
 
 }  // namespace mok

@@ -28,12 +28,6 @@
 namespace mok {
 namespace {
 
-#define MOK_TRY(expr)                  \
-    do {                               \
-        int _rc = (expr);              \
-        if (_rc != MOK_OK) return _rc; \
-    } while (0)
-
 constexpr int kMaxEvents = 512;
 constexpr int kDefaultChunkRows = 32768;
 

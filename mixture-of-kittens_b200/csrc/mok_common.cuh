@@ -30,6 +30,13 @@ int fail_cuda(const char* what, cudaError_t err);
         ::mok::note_launch();                                            \
     } while (0)
 
+// Returns a library status code from the enclosing function unless it is MOK_OK.
+#define MOK_TRY(expr)                  \
+    do {                               \
+        int _rc = (expr);              \
+        if (_rc != MOK_OK) return _rc; \
+    } while (0)
+
 void note_launch();   // counts kernel launches of this library (mok_launch_count)
 
 int sm_count();   // multiprocessors of the current device (cached per device)

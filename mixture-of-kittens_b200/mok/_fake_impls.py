@@ -133,3 +133,16 @@ def _(y_shared, combine_buffer, topk_weights):
 @torch.library.register_fake("mok::bwd_epilogue")
 def _(d_x_shared, d_x_routed_buffer):
     return torch.empty_like(d_x_shared)
+
+
+@torch.library.register_fake("mok::router_fwd")
+def _(x, w_router, bias, topk):
+    T, E = x.shape[0], w_router.shape[0]
+    return (x.new_empty((T, topk), dtype=torch.int32), x.new_empty((T, topk), dtype=torch.float32),
+            x.new_empty((T, E), dtype=torch.float32))
+
+
+@torch.library.register_fake("mok::router_bwd")
+def _(x, w_router, top_experts, router_weights, d_router_weights, has_bias):
+    E, H = w_router.shape
+    return (torch.empty_like(x), x.new_empty((E, H), dtype=torch.float32), x.new_empty((E,), dtype=torch.float32))

@@ -91,6 +91,10 @@ def lib() -> ctypes.CDLL:
         L.mok_grouped_wgrad_mxfp8.argtypes = [c_void_p] * 7 + [c_int] * 4 + [c_void_p, c_void_p]
         L.mok_grouped_gemm_mxfp8.restype = c_int
         L.mok_grouped_wgrad_mxfp8.restype = c_int
+        L.mok_router_forward.argtypes = [c_void_p] * 4 + [c_int64] + [c_int] * 4 + [c_void_p] * 5
+        L.mok_router_backward.argtypes = [c_void_p] * 5 + [c_int64] + [c_int] * 4 + [c_void_p] * 6
+        L.mok_router_forward.restype = c_int
+        L.mok_router_backward.restype = c_int
         for name in ("mok_schedule", "mok_all_gather_top_experts", "mok_barrier_all", "mok_fwd_epilogue", "mok_bwd_epilogue",
                      "mok_mxfp8_quantize", "mok_moe_forward_bf16", "mok_moe_recompute_bf16", "mok_moe_backward_bf16",
                      "mok_grouped_gemm_bf16", "mok_grouped_wgrad_bf16"):

@@ -281,8 +281,8 @@ def build_schedule(workspace: MoKWorkspace, config: MoKConfig, top_experts: torc
         raise ValueError("all_gather_top_experts_chunk_bytes must divide one rank's route-buffer bytes")
     if not top_experts.is_cuda or top_experts.device != workspace.device:
         raise ValueError("top_experts must be on the workspace CUDA device")
-    if top_experts.dtype != torch.int64:
-        raise TypeError("top_experts must have dtype torch.int64")
+    if top_experts.dtype not in (torch.int64, torch.int32):   # int32 (what the device router writes) skips a conversion
+        raise TypeError("top_experts must have dtype torch.int64 (or torch.int32)")
     if not top_experts.is_contiguous():
         raise ValueError("top_experts must be contiguous")
     if tuple(top_experts.shape) != (workspace.num_local_tokens, workspace.topk):
@@ -290,7 +290,8 @@ def build_schedule(workspace: MoKWorkspace, config: MoKConfig, top_experts: torc
     if type(num_local_experts) is not int or num_local_experts <= 0:
         raise ValueError("num_local_experts must be a positive integer")
 
-    all_gather_top_experts(top_experts.to(torch.int32), workspace.all_gather_top_experts_buffer,
+    routes = top_experts if top_experts.dtype == torch.int32 else top_experts.to(torch.int32)
+    all_gather_top_experts(routes, workspace.all_gather_top_experts_buffer,
                            workspace.all_gather_top_experts_buffer_multicast_ptr, workspace.ep_rank, chunk)
     _barrier(workspace)
     peer_rank, peer_token_idx, num_tokens, tokens_per_expert = schedule(

@@ -50,6 +50,30 @@ class _MoKLayerFunction(torch.autograd.Function):
         return d_x, d_rw, d_wsg, d_wsu, d_wsd, d_wrg, d_wru, d_wrd, None, None, None, None, None, None
 
 
+class _RouterFunction(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, w_router, bias, topk):
+        routes, weights, _logits = ops.router_fwd(x, w_router, bias, topk)
+        ctx.save_for_backward(x, w_router, routes, weights)
+        ctx.has_bias = bias is not None
+        ctx.mark_non_differentiable(routes)
+        return routes, weights
+
+    @staticmethod
+    def backward(ctx, _d_routes, d_weights):
+        x, w_router, routes, weights = ctx.saved_tensors
+        d_x, d_w, d_bias = ops.router_bwd(x, w_router, routes, weights, d_weights.contiguous(), ctx.has_bias)
+        return d_x, d_w.to(w_router.dtype), (d_bias if ctx.has_bias else None), None
+
+
+def route(x: torch.Tensor, w_router: torch.Tensor, bias: torch.Tensor | None = None, *, topk: int
+          ) -> tuple[torch.Tensor, torch.Tensor]:
+    """Differentiable softmax top-k router on the device: logits = x @ w_router.T (+ bias) in fp32, the topk largest
+    per token, weights = softmax over the selected logits.  Returns (top_experts int32 [T, topk], router_weights fp32
+    [T, topk]); gradients flow from router_weights to x, w_router ([E, H], fp32 or bf16) and bias."""
+    return _RouterFunction.apply(x, w_router, bias, topk)
+
+
 def moe_layer(x: torch.Tensor, top_experts: torch.Tensor, router_weights: torch.Tensor,
               w_shared_gate: torch.Tensor, w_shared_up: torch.Tensor, w_shared_down: torch.Tensor,
               w_routed_gate: torch.Tensor, w_routed_up: torch.Tensor, w_routed_down: torch.Tensor, *,
@@ -85,16 +109,14 @@ class MoKMoE(torch.nn.Module):
 
         def param(*shape, dtype=torch.bfloat16):
             return torch.nn.Parameter(torch.randn(*shape, device=device, dtype=torch.float32).mul_(init_std).to(dtype))
-        self.router = param(hidden_size, num_experts, dtype=torch.float32)
+        self.router = param(num_experts, hidden_size, dtype=torch.float32)
         self.w_shared_gate, self.w_shared_up = param(intermediate_size, hidden_size), param(intermediate_size, hidden_size)
         self.w_shared_down = param(hidden_size, intermediate_size)
         self.w_routed_gate, self.w_routed_up = param(e_loc, intermediate_size, hidden_size), param(e_loc, intermediate_size, hidden_size)
         self.w_routed_down = param(e_loc, hidden_size, intermediate_size)
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
-        logits = x.float() @ self.router
-        values, experts = torch.topk(logits, self.topk, dim=-1)
-        weights = torch.softmax(values, dim=-1)
-        return moe_layer(x, experts.contiguous(), weights.contiguous(), self.w_shared_gate, self.w_shared_up, self.w_shared_down,
+        experts, weights = route(x, self.router, topk=self.topk)
+        return moe_layer(x, experts, weights, self.w_shared_gate, self.w_shared_up, self.w_shared_down,
                          self.w_routed_gate, self.w_routed_up, self.w_routed_down, group=self.group, config=self.config,
                          swiglu_limit=self.swiglu_limit, recompute=self.recompute, mxfp8=self.mxfp8)

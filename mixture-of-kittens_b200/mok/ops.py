@@ -861,3 +861,83 @@ def dispatch_mlp_swiglu_combine_bwd_mxfp8(
     return (d_x_shared, d_x_routed, d_gate_shared, d_gate_q, d_gate_sc, d_up_shared, d_up_q, d_up_sc, d_hidden_shared,
             d_hidden_routed, d_y_q, d_y_sc, d_w_shared_gate, d_w_routed_gate, d_w_shared_up, d_w_routed_up, d_w_shared_down,
             d_w_routed_down)
+
+
+# ------------------------------------------------------------------------------------------------------------
+# router (no counterpart among the reference's ops: there the routes and router weights are inputs)
+# ------------------------------------------------------------------------------------------------------------
+def _router_terms(w_router: torch.Tensor, padded: int):
+    """[E, H] router weight -> bf16 (hi, lo) terms padded with zero rows to `padded` experts; lo is None for bf16 input
+    (hi + lo carries an fp32 weight to about 16 mantissa bits)."""
+    w32 = w_router.float()
+    hi = w32.to(torch.bfloat16)
+    lo = (w32 - hi.float()).to(torch.bfloat16) if w_router.dtype == torch.float32 else None
+    pad = padded - w_router.shape[0]
+    if pad:
+        hi = torch.nn.functional.pad(hi, (0, 0, 0, pad))
+        lo = torch.nn.functional.pad(lo, (0, 0, 0, pad)) if lo is not None else None
+    return hi.contiguous(), (lo.contiguous() if lo is not None else None)
+
+
+def _check_router(x: torch.Tensor, w_router: torch.Tensor, bias: torch.Tensor | None, topk: int):
+    _require(x.ndim == 2, "x must have shape (num_local_tokens, hidden_size)")
+    T, H = x.shape
+    _require(T > 0 and T % 256 == 0, "num_local_tokens must be positive and divisible by 256")
+    _require(H > 0 and H % 256 == 0, "hidden_size must be positive and divisible by 256")
+    _require(w_router.ndim == 2 and w_router.shape[1] == H, "w_router must have shape (num_experts, hidden_size)")
+    E = w_router.shape[0]
+    _require(0 < E <= 1024, "num_experts must be in [1, 1024]")
+    _require(type(topk) is int and 0 < topk <= min(E, 32), "topk must be an integer in [1, min(num_experts, 32)]")
+    _require(x.is_cuda and w_router.device == x.device, "x and w_router must be on the same CUDA device")
+    _require(x.dtype == torch.bfloat16 and x.is_contiguous(), "x must be contiguous bfloat16", TypeError)
+    _require(w_router.dtype in (torch.float32, torch.bfloat16) and w_router.is_contiguous(),
+             "w_router must be contiguous float32 or bfloat16", TypeError)
+    if bias is not None:
+        _require(tuple(bias.shape) == (E,) and bias.device == x.device, "bias must have shape (num_experts,) on the device of x")
+        _require(bias.dtype == torch.float32 and bias.is_contiguous(), "bias must be contiguous float32", TypeError)
+    return T, H, E, -(-E // 256) * 256
+
+
+@torch.library.custom_op("mok::router_fwd", mutates_args=())
+def router_fwd(x: torch.Tensor, w_router: torch.Tensor, bias: torch.Tensor | None, topk: int
+               ) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    """logits = x @ w_router.T (+ bias) in fp32, top-k (descending, ties to the lower index), softmax over the selected
+    logits.
+
+    Inputs:  x bf16 [T, H]; w_router f32 | bf16 [E, H]; bias f32 [E] | None; topk int
+    Outputs: top_experts int32 [T, topk]; router_weights f32 [T, topk]; logits f32 [T, E] (without the bias)
+    """
+    T, H, E, padded = _check_router(x, w_router, bias, topk)
+    hi, lo = _router_terms(w_router, padded)
+    logits = torch.empty((T, padded), dtype=torch.float32, device=x.device)
+    routes = torch.empty((T, topk), dtype=torch.int32, device=x.device)
+    weights = torch.empty((T, topk), dtype=torch.float32, device=x.device)
+    check(lib().mok_router_forward(ptr(x), ptr(hi), ptr(lo), ptr(bias), T, H, E, padded, topk, ptr(logits), ptr(routes),
+                                   ptr(weights), ptr(status_word(x.device)), stream_ptr(x.device)), "router_fwd")
+    return routes, weights, (logits if padded == E else logits[:, :E].contiguous())
+
+
+@torch.library.custom_op("mok::router_bwd", mutates_args=())
+def router_bwd(x: torch.Tensor, w_router: torch.Tensor, top_experts: torch.Tensor, router_weights: torch.Tensor,
+               d_router_weights: torch.Tensor, has_bias: bool) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    """Gradient of router_fwd's weights with respect to x, w_router and the bias.
+
+    Inputs:  x bf16 [T, H]; w_router [E, H]; top_experts int32 [T, topk]; router_weights, d_router_weights f32 [T, topk]
+    Outputs: d_x bf16 [T, H]; d_w_router f32 [E, H]; d_bias f32 [E] (zeros when has_bias is False)
+    """
+    _require(top_experts.ndim == 2, "top_experts must have shape (num_local_tokens, topk)")
+    topk = top_experts.shape[1]
+    T, H, E, padded = _check_router(x, w_router, None, topk)
+    for name, t, dt in (("top_experts", top_experts, torch.int32), ("router_weights", router_weights, torch.float32),
+                        ("d_router_weights", d_router_weights, torch.float32)):
+        _require(tuple(t.shape) == (T, topk) and t.device == x.device, f"{name} must have shape (num_local_tokens, topk) on the device of x")
+        _require(t.dtype == dt and t.is_contiguous(), f"{name} must be contiguous {dt}", TypeError)
+    hi, _ = _router_terms(w_router, padded)
+    d_logits = torch.empty((T, padded), dtype=torch.bfloat16, device=x.device)
+    d_x = torch.empty_like(x)
+    d_w = torch.empty((padded, H), dtype=torch.float32, device=x.device)
+    d_bias = torch.zeros((E,), dtype=torch.float32, device=x.device)
+    check(lib().mok_router_backward(ptr(x), ptr(hi), ptr(top_experts), ptr(router_weights), ptr(d_router_weights), T, H, E, padded,
+                                    topk, ptr(d_logits), ptr(d_x), ptr(d_w), ptr(d_bias) if has_bias else ptr(None),
+                                    ptr(status_word(x.device)), stream_ptr(x.device)), "router_bwd")
+    return d_x, d_w[:E].contiguous() if padded != E else d_w, d_bias

@@ -426,6 +426,31 @@ def make_rank_inputs(rank: int, num_experts: int, num_local_experts: int, topk: 
     return RankInputs(x, experts, weights, wsg, wsu, wsd, wrg, wru, wrd, d_out)
 
 
+def router_oracle(x: torch.Tensor, w_router: torch.Tensor, bias: torch.Tensor | None, topk: int):
+    """The router expression of the reference's tests (tests/utils.py:82-84) with a weight matrix in front of it:
+    logits = x @ w_router.T (+ bias), top-k, softmax over the selected logits.  float64 throughout, so that it can judge
+    near-ties.  Returns (top_experts int64 [T, k], router_weights f64 [T, k], logits f64 [T, E] without the bias)."""
+    logits = x.double() @ w_router.double().t()
+    biased = logits if bias is None else logits + bias.double()
+    values, experts = torch.topk(biased, topk, dim=-1)
+    return experts, torch.softmax(values, dim=-1), logits
+
+
+def router_bwd_oracle(x: torch.Tensor, w_router: torch.Tensor, bias: torch.Tensor | None, top_experts: torch.Tensor,
+                      d_router_weights: torch.Tensor):
+    """Gradients of router_oracle's weights for the given routes, by autograd in float64:
+    (d_x [T, H], d_w_router [E, H], d_bias [E] or None)."""
+    xd = x.double().requires_grad_(True)
+    wd = w_router.double().requires_grad_(True)
+    bd = bias.double().requires_grad_(True) if bias is not None else None
+    logits = xd @ wd.t()
+    if bd is not None:
+        logits = logits + bd
+    weights = torch.softmax(torch.gather(logits, 1, top_experts.long()), dim=-1)
+    weights.backward(d_router_weights.double())
+    return xd.grad, wd.grad, (bd.grad if bd is not None else None)
+
+
 def error_stats(reference: torch.Tensor, actual: torch.Tensor):
     """(max |diff|, sum|diff| / sum|ref|, rel-L2, cosine) — the reference metric is the first two
     (tests/utils.py:435-476); rel-L2 is the bound the acceptance criteria state."""
