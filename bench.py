@@ -548,8 +548,65 @@ def run_gemm_only(args, w):
                       "peak_burst_tflops": peaks["burst"], "peak_source": peaks["source"]}), flush=True)
 
 
+def run_router_only(args, w):
+    """`--router`: the device router (forward and backward) on the workload's tokens, hidden size, expert count and
+    top-k, next to the PyTorch expression it replaces (fp32 matmul, topk, softmax and their autograd) on the same GPU."""
+    import torch
+    import mok
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    T, H, E, K = w["T"], w["H"], w["E"], w["K"]
+    g = torch.Generator(device=dev).manual_seed(0)
+    x = torch.randn(T, H, generator=g, device=dev, dtype=torch.bfloat16)
+    wr = torch.randn(E, H, generator=g, device=dev) * H ** -0.5
+    d_w = torch.randn(T, K, generator=g, device=dev)
+
+    def timed(fn, reps=10):
+        for _ in range(3):
+            fn()
+        ev = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
+        torch.cuda.synchronize()
+        ev[0].record()
+        for _ in range(reps):
+            fn()
+        ev[1].record()
+        torch.cuda.synchronize()
+        return ev[0].elapsed_time(ev[1]) / reps
+
+    routes, weights, _ = mok.ops.router_fwd(x, wr, None, K)
+    fwd_ms = timed(lambda: mok.ops.router_fwd(x, wr, None, K))
+    bwd_ms = timed(lambda: mok.ops.router_bwd(x, wr, routes, weights, d_w, False))
+    mok.ops.check_status(dev)
+
+    def torch_fwd():
+        vals, idx = torch.topk(x.float() @ wr.t(), K, dim=-1)
+        return idx, torch.softmax(vals, dim=-1)
+
+    xg, wg = x.detach().clone().requires_grad_(True), wr.detach().clone().requires_grad_(True)
+
+    def torch_fwd_bwd():
+        vals, _ = torch.topk(xg.float() @ wg.t(), K, dim=-1)
+        torch.softmax(vals, dim=-1).backward(d_w)
+        xg.grad = wg.grad = None
+
+    t_fwd = timed(torch_fwd)
+    t_both = timed(torch_fwd_bwd)
+    idx, _ = torch_fwd()
+    agree = (idx.sort(dim=1).values == routes.long().sort(dim=1).values).all(dim=1).float().mean().item()
+    fl = 2.0 * T * H * E
+    print(json.dumps({
+        "mode": "router", "tokens": T, "hidden": H, "experts": E, "topk": K,
+        "forward_ms": fwd_ms, "backward_ms": bwd_ms,
+        # two bf16 terms of the fp32 matrix in the forward product; two products in the backward
+        "forward_tflops": 2 * fl / (fwd_ms * 1e-3) / 1e12, "backward_tflops": 2 * fl / (bwd_ms * 1e-3) / 1e12,
+        "x_bytes_over_forward_gbs": x.numel() * 2 / (fwd_ms * 1e-3) / 1e9,
+        "torch_forward_ms": t_fwd, "torch_forward_backward_ms": t_both,
+        "tokens_with_the_same_expert_set_as_torch_fp32": agree}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
+    ap.add_argument("--router", action="store_true", help="time the device router on the workload's shapes")
     ap.add_argument("--gemm-only", type=int, default=0, help="profile helper: time only the GEMM forms on this many rows")
     ap.add_argument("--gemm-experts", type=int, default=16)
     ap.add_argument("--gpus", type=int, default=1)
@@ -564,6 +621,8 @@ def main():
     w = WORKLOADS[args.workload]
     if args.gemm_only:
         run_gemm_only(args, w)
+    elif args.router:
+        run_router_only(args, w)
     elif args.impl == "reference":
         run_reference_arm(args, w)
     else:
