@@ -459,8 +459,9 @@ def run_gpu_arm(args, w):
         mok.ops.lib().mok_trace_dump(os.devnull.encode())
     sched, out, grads = step(x, dy, topk, rw)
     if tracing:
-        os.makedirs(os.path.join(ROOT, "gpurun_out"), exist_ok=True)
-        mok.ops.lib().mok_trace_dump(os.path.join(ROOT, "gpurun_out", f"trace_{args.dtype}_ep{world}_rank{rank}.txt").encode())
+        trace_dir = os.environ.get("MOK_TRACE_DIR", ROOT)   # where the phase timelines go (one file per rank)
+        os.makedirs(trace_dir, exist_ok=True)
+        mok.ops.lib().mok_trace_dump(os.path.join(trace_dir, f"trace_{args.dtype}_ep{world}_rank{rank}.txt").encode())
     del out, grads
     if mxfp8:
         forms, rows_done = time_gemm_forms_mxfp8(dev, w, e_loc, sched, qg, qd, mb)

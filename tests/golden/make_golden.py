@@ -125,7 +125,9 @@ def _worker(rank, ws, ref_root, port):
 
 
 def main():
-    ref_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) != 2:
+        sys.exit("usage: python tests/golden/make_golden.py <checkout of the reference project>")
+    ref_root = sys.argv[1]
     for i, ws in enumerate((1, 2)):
         mp.spawn(_worker, args=(ws, ref_root, 29610 + i), nprocs=ws, join=True)
     print("golden fixtures written to", HERE)
