@@ -147,3 +147,15 @@ def test_functional_argument_checks_on_cpu():
     with pytest.raises(TypeError):
         F.validate_inputs(object(), None, None, torch.zeros(1))
     assert np.array_equal(mok.ops.SUPPORTED_EP_SIZES, (1, 2, 4, 8))
+
+
+def test_header_is_plain_c():
+    """The boundary is a C ABI: the header must compile as C99 (no C++ or torch types in any signature)."""
+    import shutil
+    import subprocess
+    if shutil.which("gcc") is None:
+        pytest.skip("no C compiler")
+    header = os.path.join(ROOT, "include", "mok_b200.h")
+    r = subprocess.run(["gcc", "-std=c99", "-Wall", "-Wextra", "-Werror", "-fsyntax-only", "-x", "c", header],
+                       capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr

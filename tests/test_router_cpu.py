@@ -48,3 +48,18 @@ def test_router_shape_functions():
         d_x, d_w, d_b = torch.ops.mok.router_bwd(x, w, routes, weights, weights, False)
         assert d_x.shape == x.shape and d_x.dtype == torch.bfloat16
         assert (d_w.shape, d_w.dtype, d_b.shape) == ((24, 256), torch.float32, (24,))
+
+
+def test_two_bf16_terms_carry_an_fp32_router_matrix():
+    """`hi + lo` (both bf16) reproduces an fp32 matrix to about 16 mantissa bits, which is what keeps the device logits
+    within 2e-4 of the fp32 product; rows added as padding are zero."""
+    from mok.ops import _router_terms
+    g = torch.Generator().manual_seed(2)
+    w = torch.randn(24, 256, generator=g)
+    hi, lo = _router_terms(w, 256)
+    assert hi.shape == (256, 256) and lo.shape == (256, 256) and hi.dtype == lo.dtype == torch.bfloat16
+    assert torch.count_nonzero(hi[24:]) == 0 and torch.count_nonzero(lo[24:]) == 0
+    err = (hi[:24].float() + lo[:24].float() - w).abs() / w.abs().clamp_min(1e-30)
+    assert err.max() < 2.0 ** -15
+    hi_only, none = _router_terms(w.to(torch.bfloat16), 256)
+    assert none is None and torch.equal(hi_only[:24], w.to(torch.bfloat16))
