@@ -37,28 +37,41 @@ __device__ __forceinline__ void store_staged_rows(const uint8_t* otile, uint8_t*
 // Transposed layout of a staged bf16 tile: thread = column of the tile = row of the transpose, four blocks of 32 down
 // the column.  `out` is the transposed tile's first byte (rows `ld` apart), `scale_tile` its 512-byte scale tile.
 // Every thread of the block calls; the tile must be complete (a barrier before the call is the caller's).
+// A thread takes two adjacent columns (one 32-bit shared-memory word per row, conflict free across the warp) and two of
+// the four row blocks: threads 0..63 the blocks 0 and 1, threads 64..127 the blocks 2 and 3.
 __device__ __forceinline__ void quantize_tile_transposed(const uint8_t* tile, uint8_t* otile, int tid, uint8_t* out, long long ld,
                                                          uint8_t* scale_tile) {
-    uint32_t scale_word = 0;
-    uint8_t* mine = otile + tid * kOutPitch;
+    const int pair = tid & 63, half = tid >> 6;
+    const int col_a = 2 * pair, col_b = col_a + 1;
+    uint32_t scales_a = 0, scales_b = 0;
 #pragma unroll
-    for (int kb = 0; kb < 4; ++kb) {
-        uint32_t packed[16];
+    for (int k = 0; k < 2; ++k) {
+        const int kb = 2 * half + k;
+        uint32_t pa[16], pb[16];
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
-            const uint16_t lo = *reinterpret_cast<const uint16_t*>(tile + (kb * 32 + 2 * i) * kRowPitch + tid * 2);
-            const uint16_t hi = *reinterpret_cast<const uint16_t*>(tile + (kb * 32 + 2 * i + 1) * kRowPitch + tid * 2);
-            packed[i] = static_cast<uint32_t>(lo) | (static_cast<uint32_t>(hi) << 16);
+            const uint32_t w0 = *reinterpret_cast<const uint32_t*>(tile + (kb * 32 + 2 * i) * kRowPitch + pair * 4);
+            const uint32_t w1 = *reinterpret_cast<const uint32_t*>(tile + (kb * 32 + 2 * i + 1) * kRowPitch + pair * 4);
+            pa[i] = __byte_perm(w0, w1, 0x5410);   // low halves: column a of rows 2i, 2i + 1
+            pb[i] = __byte_perm(w0, w1, 0x7632);   // high halves: column b
         }
         uint32_t out8[8], sbyte;
-        mxfp8_quantize_block(packed, out8, sbyte);
-        scale_word |= sbyte << (kb * 8);
-        *reinterpret_cast<uint4*>(mine + kb * 32) = make_uint4(out8[0], out8[1], out8[2], out8[3]);
-        *reinterpret_cast<uint4*>(mine + kb * 32 + 16) = make_uint4(out8[4], out8[5], out8[6], out8[7]);
+        mxfp8_quantize_block(pa, out8, sbyte);
+        scales_a |= sbyte << (k * 8);
+        uint8_t* dst = otile + col_a * kOutPitch + kb * 32;
+        *reinterpret_cast<uint4*>(dst) = make_uint4(out8[0], out8[1], out8[2], out8[3]);
+        *reinterpret_cast<uint4*>(dst + 16) = make_uint4(out8[4], out8[5], out8[6], out8[7]);
+        mxfp8_quantize_block(pb, out8, sbyte);
+        scales_b |= sbyte << (k * 8);
+        dst = otile + col_b * kOutPitch + kb * 32;
+        *reinterpret_cast<uint4*>(dst) = make_uint4(out8[0], out8[1], out8[2], out8[3]);
+        *reinterpret_cast<uint4*>(dst + 16) = make_uint4(out8[4], out8[5], out8[6], out8[7]);
     }
     __syncthreads();
     store_staged_rows(otile, out, ld, tid);
-    *reinterpret_cast<uint32_t*>(scale_tile + (tid & 31) * 16 + (tid >> 5) * 4) = scale_word;
+    // scale bytes of row blocks 2 * half and 2 * half + 1 of the transposed rows col_a and col_b
+    *reinterpret_cast<uint16_t*>(scale_tile + (col_a & 31) * 16 + (col_a >> 5) * 4 + 2 * half) = static_cast<uint16_t>(scales_a);
+    *reinterpret_cast<uint16_t*>(scale_tile + (col_b & 31) * 16 + (col_b >> 5) * 4 + 2 * half) = static_cast<uint16_t>(scales_b);
 }
 
 struct QuantArgs {
