@@ -3,8 +3,8 @@ backward) over `mok.ops` (the reference's twelve `torch.ops.mok.*` custom ops pl
 from . import ops
 from . import _fake_impls  # noqa: F401  (registers shape functions for torch.compile / FakeTensor)
 from . import functional
-from .module import MoKMoE, moe_layer, route
+from .module import MoKMoE, moe_layer, quantize_routed_weights, route
 
 __version__ = "0.1.0"
 
-__all__ = ["__version__", "functional", "ops", "MoKMoE", "moe_layer", "route"]
+__all__ = ["__version__", "functional", "ops", "MoKMoE", "moe_layer", "quantize_routed_weights", "route"]

@@ -15,15 +15,20 @@ from . import functional as F
 from . import ops
 
 
+def quantize_routed_weights(w_routed_gate: torch.Tensor, w_routed_up: torch.Tensor, w_routed_down: torch.Tensor):
+    """MXFP8 copies of the routed expert weights, each as (e4m3, scales, e4m3 of the transpose, its scales): what the
+    MXFP8 forward and backward consume.  A trainer computes them once per optimizer step (or once, for inference) and
+    passes them to `moe_layer(..., quantized_weights=...)`; `MoKMoE` caches them until a weight changes."""
+    return tuple(ops.mxfp8_quantize(w, True, True) for w in (w_routed_gate, w_routed_up, w_routed_down))
+
+
 class _MoKLayerFunction(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, router_weights, w_shared_gate, w_shared_up, w_shared_down, w_routed_gate, w_routed_up, w_routed_down,
-                config, workspace, schedule, swiglu_limit, recompute, mxfp8):
+                config, workspace, schedule, swiglu_limit, recompute, mxfp8, quantized):
         weights = (w_shared_gate, w_shared_up, w_shared_down, w_routed_gate, w_routed_up, w_routed_down)
         if mxfp8:
-            qg = ops.mxfp8_quantize(w_routed_gate, True, True)
-            qu = ops.mxfp8_quantize(w_routed_up, True, True)
-            qd = ops.mxfp8_quantize(w_routed_down, True, True)
+            qg, qu, qd = quantized if quantized is not None else quantize_routed_weights(w_routed_gate, w_routed_up, w_routed_down)
             fwd_routed = ((qg[0], qg[1]), (qu[0], qu[1]), (qd[0], qd[1]))
             ctx.bwd_routed = (qg, qu, (qd[2], qd[3]))
         else:
@@ -47,7 +52,7 @@ class _MoKLayerFunction(torch.autograd.Function):
         (d_x, d_rw, d_wrg, d_wru, d_wrd, d_wsg, d_wsu, d_wsd) = F.backward(
             config, workspace, schedule, fwd_ctx, d_out.contiguous(), x, router_weights, wsg, wsu, wsd, *ctx.bwd_routed,
             swiglu_limit=swiglu_limit)
-        return d_x, d_rw, d_wsg, d_wsu, d_wsd, d_wrg, d_wru, d_wrd, None, None, None, None, None, None
+        return d_x, d_rw, d_wsg, d_wsu, d_wsd, d_wrg, d_wru, d_wrd, None, None, None, None, None, None, None
 
 
 class _RouterFunction(torch.autograd.Function):
@@ -78,16 +83,18 @@ def moe_layer(x: torch.Tensor, top_experts: torch.Tensor, router_weights: torch.
               w_shared_gate: torch.Tensor, w_shared_up: torch.Tensor, w_shared_down: torch.Tensor,
               w_routed_gate: torch.Tensor, w_routed_up: torch.Tensor, w_routed_down: torch.Tensor, *,
               group: dist.ProcessGroup | None = None, config: F.MoKConfig | None = None, swiglu_limit: float | None = None,
-              recompute: bool = False, mxfp8: bool = False) -> torch.Tensor:
-    """Differentiable MoE layer: output [T, H] bf16 from x [T, H] bf16, top_experts int64 [T, K], router_weights fp32
-    [T, K] and the bf16 expert weights of this rank.  Gradients flow to x, router_weights and all six weights."""
+              recompute: bool = False, mxfp8: bool = False, quantized_weights=None) -> torch.Tensor:
+    """Differentiable MoE layer: output [T, H] bf16 from x [T, H] bf16, top_experts int64 or int32 [T, K], router_weights fp32
+    [T, K] and the bf16 expert weights of this rank.  Gradients flow to x, router_weights and all six weights.
+    With `mxfp8=True` the routed weights are quantized inside unless `quantized_weights` (from
+    `quantize_routed_weights`) is given."""
     config = config or F.MoKConfig()
     group = group or dist.group.WORLD
     workspace = F.get_workspace(config, group, device=x.device, num_local_tokens=x.shape[0], hidden_size=x.shape[1],
                                 topk=top_experts.shape[1])
     schedule = F.build_schedule(workspace, config, top_experts, num_local_experts=w_routed_gate.shape[0])
     return _MoKLayerFunction.apply(x, router_weights, w_shared_gate, w_shared_up, w_shared_down, w_routed_gate, w_routed_up,
-                                   w_routed_down, config, workspace, schedule, swiglu_limit, recompute, mxfp8)
+                                   w_routed_down, config, workspace, schedule, swiglu_limit, recompute, mxfp8, quantized_weights)
 
 
 class MoKMoE(torch.nn.Module):
@@ -105,6 +112,7 @@ class MoKMoE(torch.nn.Module):
         self.topk, self.num_experts = topk, num_experts
         self.config = config or F.MoKConfig()
         self.swiglu_limit, self.recompute, self.mxfp8 = swiglu_limit, recompute, mxfp8
+        self._quantized = None
         e_loc = num_experts // ep
 
         def param(*shape, dtype=torch.bfloat16):
@@ -115,8 +123,18 @@ class MoKMoE(torch.nn.Module):
         self.w_routed_gate, self.w_routed_up = param(e_loc, intermediate_size, hidden_size), param(e_loc, intermediate_size, hidden_size)
         self.w_routed_down = param(e_loc, hidden_size, intermediate_size)
 
+    def _quantized_weights(self):
+        """MXFP8 copies of the routed weights, rebuilt only after one of them changed (optimizer step, load_state_dict)."""
+        params = (self.w_routed_gate, self.w_routed_up, self.w_routed_down)
+        key = tuple((p.data_ptr(), p._version) for p in params)
+        if self._quantized is None or self._quantized[0] != key:
+            with torch.no_grad():
+                self._quantized = (key, quantize_routed_weights(*params))
+        return self._quantized[1]
+
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         experts, weights = route(x, self.router, topk=self.topk)
         return moe_layer(x, experts, weights, self.w_shared_gate, self.w_shared_up, self.w_shared_down,
                          self.w_routed_gate, self.w_routed_up, self.w_routed_down, group=self.group, config=self.config,
-                         swiglu_limit=self.swiglu_limit, recompute=self.recompute, mxfp8=self.mxfp8)
+                         swiglu_limit=self.swiglu_limit, recompute=self.recompute, mxfp8=self.mxfp8,
+                         quantized_weights=self._quantized_weights() if self.mxfp8 else None)

@@ -113,3 +113,28 @@ def test_router_rejects_bad_arguments(dev):
     ):
         with pytest.raises(exc):
             mok.ops.router_fwd(**(dict(x=x, w_router=w, bias=b, topk=2) | kwargs))
+
+
+def test_module_quantizes_its_weights_once_until_they_change(dist_ctx, monkeypatch):
+    """MoKMoE(mxfp8=True) keeps the MXFP8 copies of its routed weights between calls and rebuilds them after an
+    in-place update of a weight (what an optimizer step does)."""
+    import mok
+    _, _, dev = dist_ctx
+    torch.manual_seed(4)
+    layer = mok.MoKMoE(256, 256, 8, 2, device=dev, mxfp8=True)
+    calls = []
+    original = mok.ops.mxfp8_quantize
+    monkeypatch.setattr(mok.ops, "mxfp8_quantize", lambda *a: (calls.append(1), original(*a))[1])
+    x = torch.randn(512, 256, device=dev, dtype=torch.bfloat16)
+    with torch.no_grad():
+        out1 = layer(x)
+        out2 = layer(x)
+    assert len(calls) == 3 and torch.equal(out1, out2)          # gate, up, down: once
+    with torch.no_grad():
+        layer.w_routed_down.mul_(0.5)
+        out3 = layer(x)
+    assert len(calls) == 6 and not torch.equal(out1, out3)
+    layer(x).float().sum().backward()                           # training path uses the cached copies too
+    assert len(calls) == 6 and layer.w_routed_gate.grad is not None
+    torch.cuda.synchronize()
+    mok.ops.check_status(dev)
