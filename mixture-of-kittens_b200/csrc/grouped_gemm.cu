@@ -66,6 +66,10 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_const
     volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_gen + SharedLayout::kAbort);
     int* cum = reinterpret_cast<int*>(smem_gen + SharedLayout::kCum);
 
+    // A launch for a row window behind the schedule's last row (the host sizes launches for the capacity, the row
+    // count stays on the device) leaves before anything is set up; both CTAs of every pair take the same branch.
+    if (min(p.row_end, p.tokens_per_expert == nullptr ? p.dense_rows : *p.num_tokens) <= p.row_begin) return;
+
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
     const int cta_rank = static_cast<int>(cluster_cta_rank());   // 0 = leader of the pair

@@ -63,6 +63,9 @@ mxfp8_gemm_kernel(const __grid_constant__ MapSet ms0, const __grid_constant__ Ma
     volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_gen + SharedLayout::kAbort);
     int* cum = reinterpret_cast<int*>(smem_gen + SharedLayout::kCum);
 
+    // nothing to do for a row window behind the schedule's last row: leave before anything is set up (both CTAs alike)
+    if (min(p.row_end, p.tokens_per_expert == nullptr ? p.dense_rows : *p.num_tokens) <= p.row_begin) return;
+
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
     const int cta_rank = static_cast<int>(cluster_cta_rank());
@@ -163,11 +166,10 @@ mxfp8_gemm_kernel(const __grid_constant__ MapSet ms0, const __grid_constant__ Ma
                     if (lane == 0) {
                         const uint32_t a_addr = smem_base + stage * DATA_STAGE_BYTES;
                         const uint32_t b_addr = a_addr + A_TILE_BYTES;
-                        const uint32_t s_addr = scale_base + stage * SCALE_STAGE_BYTES;
-                        // the scale columns rotate with the stage, so that the copy for this K step does not have to
-                        // wait for the MMAs of the previous one to finish reading theirs
+                        // the scale columns rotate with the stage (one slot per stage when scale_slots == STAGES)
                         const uint32_t slot = static_cast<uint32_t>(stage % p.scale_slots) * SCALE_SLOT_COLS;
                         const uint32_t sfa = sfa_tmem + slot, sfb = sfb_tmem + slot;
+                        const uint32_t s_addr = scale_base + stage * SCALE_STAGE_BYTES;
                         tmem_copy_scales_pair(sfa, umma_scale_desc(s_addr));
                         tmem_copy_scales_pair(sfb, umma_scale_desc(s_addr + SCALE_TILE_BYTES));
                         tmem_copy_scales_pair(sfb + 4, umma_scale_desc(s_addr + 2 * SCALE_TILE_BYTES));
