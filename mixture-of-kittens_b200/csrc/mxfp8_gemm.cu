@@ -225,12 +225,16 @@ mxfp8_gemm_kernel(const __grid_constant__ MapSet ms0, const __grid_constant__ Ma
                 // tensor memory back to the MMA issuer before any of it is written out.
                 uint4 packed[BN / 8];
 #pragma unroll
-                for (int c = 0; c < BN / 32; ++c) {
-                    uint32_t v[32];
-                    tmem_ld_32x32(taddr + c * 32, v);
+                for (int c = 0; c < BN / 64; ++c) {   // two loads in flight per wait
+                    uint32_t v0[32], v1[32];
+                    tmem_ld_32x32(taddr + c * 64, v0);
+                    tmem_ld_32x32(taddr + c * 64 + 32, v1);
                     tmem_ld_wait();
 #pragma unroll
-                    for (int i = 0; i < 4; ++i) packed[c * 4 + i] = pack8_bf16(&v[8 * i]);
+                    for (int i = 0; i < 4; ++i) {
+                        packed[c * 8 + i] = pack8_bf16(&v0[8 * i]);
+                        packed[c * 8 + 4 + i] = pack8_bf16(&v1[8 * i]);
+                    }
                 }
                 tc_fence_before_sync();
                 __syncwarp();
