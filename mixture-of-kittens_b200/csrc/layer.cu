@@ -205,6 +205,13 @@ bool fused_activations_enabled() {
     return !(v != nullptr && v[0] == '1');
 }
 
+// MOK_NO_FUSED_EPILOGUE=1: the MXFP8 gate / up GEMM writes bf16 gate and up, and the fused SwiGLU + quantize kernel
+// runs after it, instead of forming hidden and quantizing in the GEMM's own epilogue (same bytes either way)
+bool fused_epilogue_enabled() {
+    const char* v = getenv("MOK_NO_FUSED_EPILOGUE");
+    return !(v != nullptr && v[0] == '1');
+}
+
 // MOK_NO_WGRAD_TRIM=1 lets the weight-gradient GEMMs run over the padding rows too (for measurements; same results)
 bool wgrad_trim_enabled() {
     const char* v = getenv("MOK_NO_WGRAD_TRIM");
@@ -332,6 +339,25 @@ int gate_up_hidden_mxfp8(const mok_layer_args* a, const Span& s, cudaStream_t st
     MOK_TRY(quantize_span(a, s, a->x_routed, H, a->x_fp8, a->x_sc, a->x_fp8_t, a->x_sc_t, st));
     const Fp8Operand wg = weight_operand(a, a->w_gate_fp8, a->w_gate_sc, I, H);
     const Fp8Operand wu = weight_operand(a, a->w_up_fp8, a->w_up_sc, I, H);
+    if (fused_activations_enabled() && fused_epilogue_enabled()) {   // SwiGLU and the quantizations in the GEMM epilogue
+        const long long off = s.begin - s.base;
+        const long long sc_I = scale_tile_row_bytes(I);
+        Fp8GateUpOut o;
+        o.gate_q = static_cast<uint8_t*>(a->gate_fp8) + off * I;
+        o.gate_sc = static_cast<uint8_t*>(a->gate_sc) + (off / 128) * sc_I;
+        o.up_q = static_cast<uint8_t*>(a->up_fp8) + off * I;
+        o.up_sc = static_cast<uint8_t*>(a->up_sc) + (off / 128) * sc_I;
+        o.hidden_q = static_cast<uint8_t*>(a->hidden_fp8) + off * I;
+        o.hidden_sc = static_cast<uint8_t*>(a->hidden_sc) + (off / 128) * sc_I;
+        o.hidden_qt = static_cast<uint8_t*>(a->hidden_fp8_t) + off;
+        o.hidden_sct = static_cast<uint8_t*>(a->hidden_sc_t) + (off / 128) * 512;
+        o.sc_row_tile_stride = sc_I;
+        o.qt_ld = a->macrobatch_size;
+        o.sct_row_tile_stride = scale_tile_row_bytes(a->macrobatch_size);
+        o.has_limit = a->has_swiglu_limit != 0;
+        o.limit = a->swiglu_limit;
+        return launch_fp8_gate_up_fused(routed_problem(a, s), act_rows(a, a->x_fp8, a->x_sc, H, s), H, wg, wu, I, o, st);
+    }
     MOK_TRY(launch_fp8_rows_gemm(routed_problem(a, s), act_rows(a, a->x_fp8, a->x_sc, H, s), H, wg, &wu,
                                  rows_bf16(a->gate_routed, s, I), rows_bf16(a->up_routed, s, I), I, st));
     if (fused_activations_enabled()) {   // one pass: e4m3 gate, up, and hidden in both layouts

@@ -10,7 +10,9 @@
 // Both operands are K-major; the dgrad and wgrad forms use transposed-quantized copies of weights / activations
 // (the role MXFP8 plays in the reference grouped GEMM, csrc/megakernel/grouped_gemm.cuh:222-249).
 #include "gemm_tiles.cuh"
+#include "mxfp8.cuh"
 #include "mxfp8_gemm.cuh"
+#include "swiglu_math.cuh"
 
 namespace mok {
 namespace {
@@ -48,9 +50,106 @@ struct MapSet {
     CUtensorMap a, sfa, b, sfb;
 };
 
-template <int MODE>
+// ---- fused gate / up epilogue ---------------------------------------------------------------------------------------
+// Device copy of Fp8GateUpOut.  With `enabled` a rows-form tile holds gate columns [c0, c0 + 128) in accumulator
+// columns [0, 128) (CTA 0 stages the gate weights) and the same up columns in [128, 256) (CTA 1 stages the up weights).
+struct FusedOut {
+    uint8_t *gate_q, *gate_sc, *up_q, *up_sc, *hid_q, *hid_sc, *hid_qt, *hid_sct;
+    long long sc_row_tile_stride, qt_ld, sct_row_tile_stride;
+    int cols;      // N of gate / up = row length of the e4m3 outputs
+    int enabled, clamp;
+    float limit;
+};
+
+// One warp = 32 rows of the tile (buffer rows R0 .. R0 + 31, all in one 128-row tile), `packed` = this lane's row:
+// vectors [0, 16) gate, [16, 32) up, already rounded to bf16.
+template <bool CLAMP>
+__device__ __forceinline__ void fused_gate_up_epilogue(const FusedOut& f, const uint4 (&packed)[32], uint8_t* patch, long long R0,
+                                                       int col0, int quarter, int lane) {
+    const long long row_tile = R0 >> 7;
+    const int col_tile = col0 >> 7;
+    const long long sc_off = row_tile * f.sc_row_tile_stride + static_cast<long long>(col_tile) * 512 + lane * 16 + quarter * 4;
+    const long long q_off = R0 * f.cols + col0;
+    // block by block (32 columns), so that the gate / up registers die as the bytes are produced
+    uint4 h[16], gate_bytes[8], up_bytes[8], hid_bytes[8];
+    uint32_t gate_scales = 0, up_scales = 0, hid_scales = 0;
+#pragma unroll
+    for (int b = 0; b < 4; ++b) {
+        uint32_t g[16], u[16], hb[16], out8[8], sbyte;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const uint4 gv = packed[4 * b + i], uv = packed[16 + 4 * b + i];
+            g[4 * i] = gv.x; g[4 * i + 1] = gv.y; g[4 * i + 2] = gv.z; g[4 * i + 3] = gv.w;
+            u[4 * i] = uv.x; u[4 * i + 1] = uv.y; u[4 * i + 2] = uv.z; u[4 * i + 3] = uv.w;
+        }
+#pragma unroll
+        for (int i = 0; i < 16; ++i) hb[i] = swiglu_pair<CLAMP>(g[i], u[i], f.limit);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) h[4 * b + i] = make_uint4(hb[4 * i], hb[4 * i + 1], hb[4 * i + 2], hb[4 * i + 3]);
+        mxfp8_quantize_block(g, out8, sbyte);
+        gate_scales |= sbyte << (8 * b);
+        gate_bytes[2 * b] = make_uint4(out8[0], out8[1], out8[2], out8[3]);
+        gate_bytes[2 * b + 1] = make_uint4(out8[4], out8[5], out8[6], out8[7]);
+        mxfp8_quantize_block(u, out8, sbyte);
+        up_scales |= sbyte << (8 * b);
+        up_bytes[2 * b] = make_uint4(out8[0], out8[1], out8[2], out8[3]);
+        up_bytes[2 * b + 1] = make_uint4(out8[4], out8[5], out8[6], out8[7]);
+        mxfp8_quantize_block(hb, out8, sbyte);
+        hid_scales |= sbyte << (8 * b);
+        hid_bytes[2 * b] = make_uint4(out8[0], out8[1], out8[2], out8[3]);
+        hid_bytes[2 * b + 1] = make_uint4(out8[4], out8[5], out8[6], out8[7]);
+    }
+    *reinterpret_cast<uint32_t*>(f.gate_sc + sc_off) = gate_scales;
+    *reinterpret_cast<uint32_t*>(f.up_sc + sc_off) = up_scales;
+    *reinterpret_cast<uint32_t*>(f.hid_sc + sc_off) = hid_scales;
+    // 128 bytes per row = 64 two-byte elements for the staging helper: full 128-byte lines
+    const long long ld2 = f.cols / 2;
+    epilogue_store_packed_64cols(patch, gate_bytes, reinterpret_cast<bf16*>(f.gate_q + q_off), ld2, lane);
+    epilogue_store_packed_64cols(patch, up_bytes, reinterpret_cast<bf16*>(f.up_q + q_off), ld2, lane);
+    epilogue_store_packed_64cols(patch, hid_bytes, reinterpret_cast<bf16*>(f.hid_q + q_off), ld2, lane);
+
+    // transposed layout: for one column the warp's 32 rows are exactly one block of 32; two columns per word
+    uint8_t* sct = f.hid_sct + col_tile * f.sct_row_tile_stride + row_tile * 512 + quarter;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+        const uint32_t words[4] = {h[i].x, h[i].y, h[i].z, h[i].w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int c = 8 * i + 2 * j;   // columns c, c + 1 of the tile
+            const float2 val = unpack_bf16x2(words[j]);
+            float a0 = fabsf(val.x), a1 = fabsf(val.y);
+#pragma unroll
+            for (int off = 16; off > 0; off >>= 1) {
+                a0 = fmaxf(a0, __shfl_xor_sync(0xffffffffu, a0, off));
+                a1 = fmaxf(a1, __shfl_xor_sync(0xffffffffu, a1, off));
+            }
+            const float s0 = fmaxf(a0 * 0.002232142857f, 0.000000000001f), s1 = fmaxf(a1 * 0.002232142857f, 0.000000000001f);
+            uint16_t e8;
+            asm volatile("cvt.rp.satfinite.ue8m0x2.f32 %0, %1, %2;" : "=h"(e8) : "f"(s1), "f"(s0));   // low byte: s0
+            const uint32_t sb0 = e8 & 0xFFu, sb1 = (e8 >> 8) & 0xFFu;
+            const float inv0 = __uint_as_float((254u - sb0) << 23), inv1 = __uint_as_float((254u - sb1) << 23);
+            uint16_t q2;
+            asm volatile("cvt.rn.satfinite.e4m3x2.f32 %0, %2, %1;" : "=h"(q2) : "f"(val.x * inv0), "f"(val.y * inv1));
+            patch[c * 32 + lane] = static_cast<uint8_t>(q2 & 0xFFu);
+            patch[(c + 1) * 32 + lane] = static_cast<uint8_t>(q2 >> 8);
+            if (lane == (c & 31)) sct[(c & 31) * 16 + (c >> 5) * 4] = static_cast<uint8_t>(sb0);
+            if (lane == ((c + 1) & 31)) sct[((c + 1) & 31) * 16 + ((c + 1) >> 5) * 4] = static_cast<uint8_t>(sb1);
+        }
+    }
+    __syncwarp();
+    uint8_t* qt = f.hid_qt + static_cast<long long>(col0) * f.qt_ld + R0;
+#pragma unroll
+    for (int it = 0; it < 8; ++it) {   // 16 columns per store instruction, 32 bytes (the warp's rows) each
+        const int c = it * 16 + (lane >> 1), half = lane & 1;
+        *reinterpret_cast<uint4*>(qt + static_cast<long long>(c) * f.qt_ld + half * 16) =
+            *reinterpret_cast<const uint4*>(patch + c * 32 + half * 16);
+    }
+    __syncwarp();
+}
+
+template <int MODE, bool FUSED>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
-mxfp8_gemm_kernel(const __grid_constant__ MapSet ms0, const __grid_constant__ MapSet ms1, const KernelParams p) {
+mxfp8_gemm_kernel(const __grid_constant__ MapSet ms0, const __grid_constant__ MapSet ms1, const KernelParams p, const FusedOut f) {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
@@ -127,10 +226,18 @@ mxfp8_gemm_kernel(const __grid_constant__ MapSet ms0, const __grid_constant__ Ma
                         const int row = tile.row0 - p.row_begin + cta_rank * BM_CTA;
                         tma_load_4d_pair(a_dst, &am.a, full, kt * BK, row, 0, 0);
                         tma_load_4d_pair(s_dst, &am.sfa, full, 0, kt, row / 128, 0);
-                        tma_load_4d_pair(b_dst, &bm.b, full, kt * BK, tile.n0 + cta_rank * BN_CTA, tile.expert, 0);
-                        const int sfb_row = tile.expert * p.n_tiles_per_expert + tile.n0 / 128;
-                        tma_load_4d_pair(s_dst + SCALE_TILE_BYTES, &bm.sfb, full, 0, kt, sfb_row, 0);
-                        tma_load_4d_pair(s_dst + 2 * SCALE_TILE_BYTES, &bm.sfb, full, 0, kt, sfb_row + 1, 0);
+                        if (FUSED) {   // CTA 0 stages 128 gate rows, CTA 1 the same 128 up rows; both need both scale tiles
+                            const int col0 = tile.n0 / 2;
+                            tma_load_4d_pair(b_dst, cta_rank ? &ms1.b : &ms0.b, full, kt * BK, col0, tile.expert, 0);
+                            const int sfb_row = tile.expert * p.n_tiles_per_expert + col0 / 128;
+                            tma_load_4d_pair(s_dst + SCALE_TILE_BYTES, &ms0.sfb, full, 0, kt, sfb_row, 0);
+                            tma_load_4d_pair(s_dst + 2 * SCALE_TILE_BYTES, &ms1.sfb, full, 0, kt, sfb_row, 0);
+                        } else {
+                            tma_load_4d_pair(b_dst, &bm.b, full, kt * BK, tile.n0 + cta_rank * BN_CTA, tile.expert, 0);
+                            const int sfb_row = tile.expert * p.n_tiles_per_expert + tile.n0 / 128;
+                            tma_load_4d_pair(s_dst + SCALE_TILE_BYTES, &bm.sfb, full, 0, kt, sfb_row, 0);
+                            tma_load_4d_pair(s_dst + 2 * SCALE_TILE_BYTES, &bm.sfb, full, 0, kt, sfb_row + 1, 0);
+                        }
                     } else {
                         const int kcol = tile.row0 + kb * BK - p.row_begin;   // column of the transposed activations
                         tma_load_4d_pair(a_dst, &ms0.a, full, kcol, tile.m0 + cta_rank * BM_CTA, 0, 0);
@@ -239,8 +346,15 @@ mxfp8_gemm_kernel(const __grid_constant__ MapSet ms0, const __grid_constant__ Ma
                 tc_fence_before_sync();
                 __syncwarp();
                 if (lane == 0) mbar_arrive_leader(bar_tmem_empty);
+                if (MODE == MODE_ROWS && FUSED) {
+                    const long long R0 = tile.row0 - p.row_begin + cta_rank * BM_CTA + quarter * 32;
+                    if (f.clamp) fused_gate_up_epilogue<true>(f, packed, patch, R0, tile.n0 / 2, quarter, lane);
+                    else fused_gate_up_epilogue<false>(f, packed, patch, R0, tile.n0 / 2, quarter, lane);
+                } else {
 #pragma unroll
-                for (int c = 0; c < BN / 64; ++c) epilogue_store_packed_64cols(patch, &packed[c * 8], warp_out + c * 64, p.ldd, lane);
+                    for (int c = 0; c < BN / 64; ++c)
+                        epilogue_store_packed_64cols(patch, &packed[c * 8], warp_out + c * 64, p.ldd, lane);
+                }
             }
             ++iter;
         }
@@ -313,12 +427,13 @@ int scale_slots() {
     return slots;
 }
 
-template <int MODE>
-int launch(const MapSet& ms0, const MapSet& ms1, KernelParams kp, int max_tiles, cudaStream_t stream) {
+template <int MODE, bool FUSED = false>
+int launch(const MapSet& ms0, const MapSet& ms1, KernelParams kp, int max_tiles, cudaStream_t stream,
+           const FusedOut& fused = FusedOut{}) {
     static int resident_pairs[16] = {0};
     kp.scale_slots = scale_slots();
-    return launch_pairs(mxfp8_gemm_kernel<MODE>, "mxfp8_gemm_kernel", resident_pairs, smem_bytes(kp.num_experts), max_tiles,
-                        stream, ms0, ms1, kp);
+    return launch_pairs(mxfp8_gemm_kernel<MODE, FUSED>, "mxfp8_gemm_kernel", resident_pairs, smem_bytes(kp.num_experts), max_tiles,
+                        stream, ms0, ms1, kp, fused);
 }
 
 
@@ -341,6 +456,43 @@ int launch_fp8_rows_gemm(const GemmProblem& pb, const Fp8Operand& A, int K, cons
     kp.D1 = static_cast<bf16*>(D1);
     kp.ldd = N;
     return launch<MODE_ROWS>(ms0, ms1, kp, ((pb.row_end - pb.row_begin) / BM) * kp.n_blocks * kp.n_sets, stream);
+}
+
+int launch_fp8_gate_up_fused(const GemmProblem& pb, const Fp8Operand& A, int K, const Fp8Operand& Wg, const Fp8Operand& Wu, int N,
+                             const Fp8GateUpOut& out, cudaStream_t stream) {
+    int rc = check_problem(pb);
+    if (rc != MOK_OK) return rc;
+    if (K <= 0 || N <= 0 || K % BK != 0 || N % 128 != 0) return MOK_ERR_INVALID_ARGUMENT;
+    if (!out.gate_q || !out.gate_sc || !out.up_q || !out.up_sc || !out.hidden_q || !out.hidden_sc || !out.hidden_qt ||
+        !out.hidden_sct || out.qt_ld <= 0 || out.qt_ld % 16 != 0)
+        return MOK_ERR_INVALID_ARGUMENT;
+    MapSet ms0, ms1;
+    if ((rc = fill_set(&ms0, A, 1, Wg, pb.num_experts)) != MOK_OK) return rc;
+    if ((rc = fill_set(&ms1, A, 1, Wu, pb.num_experts)) != MOK_OK) return rc;
+    KernelParams kp = base_params(pb);
+    kp.n_blocks = N / 128;              // one tile per 128 gate columns + the same 128 up columns
+    kp.k_blocks = K / BK;
+    kp.n_tiles_per_expert = N / 128;
+    kp.D0 = nullptr;
+    kp.D1 = nullptr;
+    kp.ldd = N;
+    FusedOut f{};
+    f.gate_q = static_cast<uint8_t*>(out.gate_q);
+    f.gate_sc = static_cast<uint8_t*>(out.gate_sc);
+    f.up_q = static_cast<uint8_t*>(out.up_q);
+    f.up_sc = static_cast<uint8_t*>(out.up_sc);
+    f.hid_q = static_cast<uint8_t*>(out.hidden_q);
+    f.hid_sc = static_cast<uint8_t*>(out.hidden_sc);
+    f.hid_qt = static_cast<uint8_t*>(out.hidden_qt);
+    f.hid_sct = static_cast<uint8_t*>(out.hidden_sct);
+    f.sc_row_tile_stride = out.sc_row_tile_stride;
+    f.qt_ld = out.qt_ld;
+    f.sct_row_tile_stride = out.sct_row_tile_stride;
+    f.cols = N;
+    f.enabled = 1;
+    f.clamp = out.has_limit ? 1 : 0;
+    f.limit = out.limit;
+    return launch<MODE_ROWS, true>(ms0, ms1, kp, ((pb.row_end - pb.row_begin) / BM) * kp.n_blocks, stream, f);
 }
 
 int launch_fp8_rows_gemm_dual(const GemmProblem& pb, const Fp8Operand& A0, const Fp8Operand& A1, int K, const Fp8Operand& B0,

@@ -156,15 +156,20 @@ def test_fused_activation_kernels_equal_the_separate_ones(dist_ctx, monkeypatch,
     config = mok.functional.MoKConfig(minibatch_size=256, macrobatch_size=1024)   # three windows: the ring is covered too
     inp = O.make_rank_inputs(0, E, E, K, T, H, I)
     monkeypatch.setenv("MOK_NO_FUSED_ACT", "1")
-    out_a, grads_a = _run_mxfp8_layer(dist_ctx, inp, E, config, limit)
+    out_a, grads_a = _run_mxfp8_layer(dist_ctx, inp, E, config, limit)                 # separate kernels
     monkeypatch.delenv("MOK_NO_FUSED_ACT")
-    out_b, grads_b = _run_mxfp8_layer(dist_ctx, inp, E, config, limit)
-    assert torch.equal(out_a, out_b)
-    for name, a, b in zip(FIELDS, grads_a, grads_b):
-        if name == "d_router_weights":
-            torch.testing.assert_close(a, b, rtol=1e-4, atol=1e-5)
-        else:
-            assert torch.equal(a, b), f"{name} differs between the fused and the separate activation kernels"
+    monkeypatch.setenv("MOK_NO_FUSED_EPILOGUE", "1")
+    variants = [("fused activation kernels", _run_mxfp8_layer(dist_ctx, inp, E, config, limit))]
+    monkeypatch.delenv("MOK_NO_FUSED_EPILOGUE")
+    # default: the forward SwiGLU and its quantizations run in the epilogue of the gate / up GEMM
+    variants.append(("fused GEMM epilogue", _run_mxfp8_layer(dist_ctx, inp, E, config, limit)))
+    for what, (out_b, grads_b) in variants:
+        assert torch.equal(out_a, out_b), what
+        for name, a, b in zip(FIELDS, grads_a, grads_b):
+            if name == "d_router_weights":
+                torch.testing.assert_close(a, b, rtol=1e-4, atol=1e-5)
+            else:
+                assert torch.equal(a, b), f"{name} differs between the separate kernels and the {what}"
 
 
 @pytest.mark.parametrize("counts,M,N", [(None, 256, 256), ([256, 0, 768], 256, 512), ([512, 512], 512, 256)])
