@@ -50,8 +50,9 @@ struct Tile {
 
 // Tile t of the static list.  rows: m tile major, then output set, then n tile, so that the tiles running at one
 // time share an expert's weights in L2.  wgrad: expert major.  Returns false for tiles without work.
+// (host-callable too: tests/tile_math_host.cu walks the tile lists on the CPU)
 template <int MODE, int BK>
-__device__ __forceinline__ bool decode_tile(const KernelParams& p, const int* cum, int lo, int hi, int t, Tile& tile) {
+__host__ __device__ __forceinline__ bool decode_tile(const KernelParams& p, const int* cum, int lo, int hi, int t, Tile& tile) {
     if (MODE == MODE_ROWS) {
         const int per_m = p.n_blocks * p.n_sets;
         const int mt = t / per_m;
@@ -94,7 +95,7 @@ __device__ __forceinline__ bool decode_tile(const KernelParams& p, const int* cu
 }
 
 template <int MODE>
-__device__ __forceinline__ int total_tiles(const KernelParams& p, int lo, int hi) {
+__host__ __device__ __forceinline__ int total_tiles(const KernelParams& p, int lo, int hi) {
     if (hi <= lo) return 0;
     return MODE == MODE_ROWS ? ((hi - lo) / BM) * p.n_blocks * p.n_sets : p.num_experts * p.m_blocks_w * p.n_blocks;
 }
