@@ -135,16 +135,18 @@ int mok_combine_rows(const uint64_t* dst_ptrs, const uint64_t* scalar_ptrs, int 
 /*
  * out[t] = bf16(y_shared[t] + sum_k w[t,k] * combine[t*K+k]) with k ascending in fp32.
  * Replaces: fwd_epilogue_kernel, csrc/utils.cuh:43-95 (op mok/ops.py:1279-1313).  y_shared may be NULL (treated as 0).
+ * `status` (may be NULL) is the device status word of the layer calls: when it holds any MOK_STATUS_* bit the routed
+ * slots cannot be trusted (the reference traps in that situation, csrc/scheduler.cuh:86) and `out` is filled with NaN.
  */
 int mok_fwd_epilogue(const void* y_shared, const void* combine_buffer, const float* topk_weights, void* out,
-                     int64_t num_local_tokens, int hidden, int topk, mok_stream_t stream);
+                     int64_t num_local_tokens, int hidden, int topk, const uint32_t* status, mok_stream_t stream);
 
 /*
  * d_x[t] = bf16(d_x_shared[t] + sum_k d_x_routed[t*K+k]).  Replaces: bwd_epilogue_kernel,
- * csrc/utils.cuh:140-176 (op mok/ops.py:1316-1349).  d_x_shared may be NULL.
+ * csrc/utils.cuh:140-176 (op mok/ops.py:1316-1349).  d_x_shared may be NULL.  `status` as for mok_fwd_epilogue.
  */
 int mok_bwd_epilogue(const void* d_x_shared, const void* d_x_routed_buffer, void* out,
-                     int64_t num_local_tokens, int hidden, int topk, mok_stream_t stream);
+                     int64_t num_local_tokens, int hidden, int topk, const uint32_t* status, mok_stream_t stream);
 
 /*
  * bf16 [E, M, N] -> e4m3 + e8m0 scale per 32 elements along the row, optionally also of the transpose.

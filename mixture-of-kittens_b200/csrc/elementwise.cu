@@ -74,12 +74,21 @@ __device__ __forceinline__ void fma_vec(float (&acc)[8], uint4 v, float w) {
 }
 
 // out[t] = bf16(shared[t] + sum_k w[t,k] * routed[t*K + k]), k ascending; WEIGHTED = false uses w = 1.
+// With a status word that holds any error bit (schedule overflow dropped rows, a wait ran out, a bad schedule entry)
+// the routed slots may hold stale or partial data: the whole output becomes NaN instead, so the failure cannot be
+// trained through unnoticed; no host synchronisation is involved.
 template <bool WEIGHTED>
 __global__ void __launch_bounds__(256) epilogue_kernel(const uint4* __restrict__ shared, const uint4* __restrict__ routed,
                                                         const float* __restrict__ weights, uint4* __restrict__ out,
-                                                        long long tokens, int vec_per_row, int topk) {
+                                                        long long tokens, int vec_per_row, int topk,
+                                                        const uint32_t* __restrict__ status) {
     const long long n = tokens * vec_per_row;
     const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+    if (status != nullptr && *status != 0u) {
+        const uint4 nan4 = make_uint4(0x7FC07FC0u, 0x7FC07FC0u, 0x7FC07FC0u, 0x7FC07FC0u);   // bf16 quiet NaNs
+        for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride) out[i] = nan4;
+        return;
+    }
     for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride) {
         const long long t = i / vec_per_row;
         const int v = static_cast<int>(i - t * vec_per_row);
@@ -219,7 +228,7 @@ int launch_zero_empty_wgrads(const int32_t* tokens_per_expert, int num_experts, 
 }  // namespace mok
 
 extern "C" int mok_fwd_epilogue(const void* y_shared, const void* combine_buffer, const float* topk_weights, void* out,
-                                int64_t num_local_tokens, int hidden, int topk, mok_stream_t stream) {
+                                int64_t num_local_tokens, int hidden, int topk, const uint32_t* status, mok_stream_t stream) {
     using namespace mok;
     if (combine_buffer == nullptr || topk_weights == nullptr || out == nullptr || num_local_tokens <= 0 || hidden <= 0 ||
         hidden % 8 != 0 || topk <= 0)
@@ -228,13 +237,13 @@ extern "C" int mok_fwd_epilogue(const void* y_shared, const void* combine_buffer
     const int grid = stream_grid(num_local_tokens * vec, 256);
     epilogue_kernel<true><<<grid, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
         static_cast<const uint4*>(y_shared), static_cast<const uint4*>(combine_buffer), topk_weights, static_cast<uint4*>(out),
-        num_local_tokens, vec, topk);
+        num_local_tokens, vec, topk, status);
     MOK_LAUNCH_CHECK("fwd_epilogue_kernel");
     return MOK_OK;
 }
 
 extern "C" int mok_bwd_epilogue(const void* d_x_shared, const void* d_x_routed_buffer, void* out, int64_t num_local_tokens,
-                                int hidden, int topk, mok_stream_t stream) {
+                                int hidden, int topk, const uint32_t* status, mok_stream_t stream) {
     using namespace mok;
     if (d_x_routed_buffer == nullptr || out == nullptr || num_local_tokens <= 0 || hidden <= 0 || hidden % 8 != 0 || topk <= 0)
         return MOK_ERR_INVALID_ARGUMENT;
@@ -242,7 +251,7 @@ extern "C" int mok_bwd_epilogue(const void* d_x_shared, const void* d_x_routed_b
     const int grid = stream_grid(num_local_tokens * vec, 256);
     epilogue_kernel<false><<<grid, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
         static_cast<const uint4*>(d_x_shared), static_cast<const uint4*>(d_x_routed_buffer), nullptr, static_cast<uint4*>(out),
-        num_local_tokens, vec, topk);
+        num_local_tokens, vec, topk, status);
     MOK_LAUNCH_CHECK("bwd_epilogue_kernel");
     return MOK_OK;
 }

@@ -6,10 +6,10 @@
 // buffers hold afterwards, and backward recomputes gate / up / hidden for windows >= 1 before using them
 // (reference: csrc/megakernel/forward.cuh:117-129,202-209 and backward.cuh:147-176,296-329).
 //
-// Overlap of NVLink traffic with the GEMMs: a window is cut into chunks of rows (a multiple of the minibatch
-// size).  Dispatch and combine kernels run on a second, internal stream with a bounded number of CTAs
-// (`num_comm_sms` x 8; they need no shared memory, so they share SMs with the resident GEMM CTAs), the GEMM /
-// SwiGLU kernels run on the caller's stream, and CUDA events at chunk granularity order them:
+// Overlap of NVLink traffic with the GEMMs: a window is cut into chunks of eight minibatches.  Dispatch and
+// combine kernels run on a second, internal stream with a bounded number of CTAs (`num_comm_sms` x 8; they need
+// no shared memory, so they share SMs with the resident GEMM CTAs), the GEMM / SwiGLU kernels run on the
+// caller's stream, and CUDA events at chunk granularity order them:
 //     comm:  dispatch(c) ------> record d[c]            wait y[c] -> combine(c)
 //     main:            wait d[c] -> GEMMs(c) -> record y[c]
 // Dispatch runs two chunks ahead.  The internal stream is forked from and joined back into the caller's stream
@@ -29,7 +29,7 @@ namespace mok {
 namespace {
 
 constexpr int kMaxEvents = 512;
-constexpr int kDefaultChunkRows = 32768;
+constexpr int kMinibatchesPerChunk = 8;
 
 struct DeviceStreams {
     cudaStream_t comm = nullptr;
@@ -38,12 +38,15 @@ struct DeviceStreams {
     bool ready = false;
 };
 
-// One helper stream and an event pool per device, created on first use (single host thread per device).
-int streams_for_current_device(DeviceStreams** out) {
+// One helper stream and an event pool per device, created on first use (single host thread per device).  The
+// caller's stream must belong to the current device: the helper stream and the events are the current device's.
+int streams_for_current_device(cudaStream_t caller, DeviceStreams** out) {
     static DeviceStreams table[16];
-    int dev = 0;
+    int dev = 0, stream_dev = 0;
     MOK_CUDA_CHECK(cudaGetDevice(&dev));
     if (dev < 0 || dev >= 16) return MOK_ERR_UNSUPPORTED;
+    MOK_CUDA_CHECK(cudaStreamGetDevice(caller, &stream_dev));
+    if (stream_dev != dev) return MOK_ERR_INVALID_ARGUMENT;
     DeviceStreams& d = table[dev];
     if (!d.ready) {
         int least = 0, greatest = 0;
@@ -69,6 +72,26 @@ int order_after(DeviceStreams* d, cudaStream_t signaller, cudaStream_t waiter) {
     MOK_CUDA_CHECK(cudaStreamWaitEvent(waiter, e, 0));
     return MOK_OK;
 }
+
+// Forks the internal stream off the caller's stream and guarantees the join: if an entry point returns early (a
+// launch failed part-way), work already queued on the internal stream may still read and write the caller's buffers,
+// so the caller's stream is made to wait for it before control goes back (after a regular join this is a no-op wait).
+struct CommFork {
+    DeviceStreams* d = nullptr;
+    cudaStream_t caller = nullptr;
+    int start(cudaStream_t s, DeviceStreams** out) {
+        MOK_TRY(streams_for_current_device(s, out));
+        MOK_TRY(order_after(*out, s, (*out)->comm));
+        d = *out;
+        caller = s;
+        return MOK_OK;
+    }
+    ~CommFork() {
+        if (d == nullptr) return;
+        cudaEvent_t e = next_event(d);
+        if (cudaEventRecord(e, d->comm) == cudaSuccess) (void)cudaStreamWaitEvent(caller, e, 0);
+    }
+};
 
 // ---- optional phase timeline (MOK_TRACE=1): CUDA events around every pull / compute / push / wgrad phase ---------
 struct TraceRecord {
@@ -105,16 +128,21 @@ bool overlap_enabled() {
     return !(v != nullptr && v[0] == '1');
 }
 
+// Rows handed from dispatch to the GEMMs to combine in one piece: kMinibatchesPerChunk minibatches, so the caller's
+// minibatch_size sets the hand-over granularity (the default 4096 gives 32768-row chunks, the size that measured best
+// on the DeepSeek-V3-shaped layer).  MOK_CHUNK_ROWS overrides the row count (rounded up to whole minibatches).
 int chunk_rows_for(const mok_layer_args* a) {
-    int rows = kDefaultChunkRows;
+    long long rows = static_cast<long long>(kMinibatchesPerChunk) * a->minibatch_size;
     if (const char* v = getenv("MOK_CHUNK_ROWS")) {
         const int r = atoi(v);
         if (r > 0) rows = r;
     }
     rows = (rows + a->minibatch_size - 1) / a->minibatch_size * a->minibatch_size;
     // never more than ~100 chunks per window: events and launches stay bounded
-    const int min_rows = (a->macrobatch_size / 100 + a->minibatch_size) / a->minibatch_size * a->minibatch_size;
-    return rows < min_rows ? min_rows : rows;
+    const long long min_rows = (a->macrobatch_size / 100 + a->minibatch_size) / a->minibatch_size * a->minibatch_size;
+    if (rows < min_rows) rows = min_rows;
+    if (rows > a->macrobatch_size) rows = a->macrobatch_size;
+    return static_cast<int>(rows);
 }
 
 int check_common(const mok_layer_args* a, bool fp8 = false) {
@@ -456,10 +484,8 @@ extern "C" int mok_moe_forward_bf16(const mok_layer_args* a, mok_stream_t stream
     cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
     const bool overlapped = overlap_enabled();
     DeviceStreams* d = nullptr;
-    if (overlapped) {
-        MOK_TRY(streams_for_current_device(&d));
-        MOK_TRY(order_after(d, s, d->comm));   // fork: the internal stream starts after the caller's earlier work
-    }
+    CommFork fork;   // the internal stream starts after the caller's earlier work and is joined on every way out
+    if (overlapped) MOK_TRY(fork.start(s, &d));
     const int H = a->hidden, I = a->intermediate;
     if (a->w_shared_gate) {   // runs on the caller's stream while the first chunks are being pulled
         MOK_TRY(shared_up_to_hidden(a, s));
@@ -517,10 +543,8 @@ extern "C" int mok_moe_backward_bf16(const mok_layer_args* a, mok_stream_t strea
     const bool clamp = a->has_swiglu_limit != 0;
     const bool overlapped = overlap_enabled();
     DeviceStreams* d = nullptr;
-    if (overlapped) {
-        MOK_TRY(streams_for_current_device(&d));
-        MOK_TRY(order_after(d, s, d->comm));
-    }
+    CommFork fork;
+    if (overlapped) MOK_TRY(fork.start(s, &d));
 
     if (shared) {
         const int ts = trace_begin("shared_bwd", 0, false, s);
@@ -590,10 +614,8 @@ extern "C" int mok_moe_forward_mxfp8(const mok_layer_args* a, mok_stream_t strea
     cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
     const bool overlapped = overlap_enabled();
     DeviceStreams* d = nullptr;
-    if (overlapped) {
-        MOK_TRY(streams_for_current_device(&d));
-        MOK_TRY(order_after(d, s, d->comm));
-    }
+    CommFork fork;
+    if (overlapped) MOK_TRY(fork.start(s, &d));
     const int H = a->hidden, I = a->intermediate;
     if (a->w_shared_gate) {
         MOK_TRY(shared_up_to_hidden(a, s));
@@ -657,10 +679,8 @@ extern "C" int mok_moe_backward_mxfp8(const mok_layer_args* a, mok_stream_t stre
     const bool clamp = a->has_swiglu_limit != 0;
     const bool overlapped = overlap_enabled();
     DeviceStreams* d = nullptr;
-    if (overlapped) {
-        MOK_TRY(streams_for_current_device(&d));
-        MOK_TRY(order_after(d, s, d->comm));
-    }
+    CommFork fork;
+    if (overlapped) MOK_TRY(fork.start(s, &d));
     if (shared) {
         const int ts = trace_begin("shared_bwd", 0, false, s);
         MOK_TRY(shared_backward(a, s));

@@ -13,7 +13,8 @@ def _sc(t, rows, cols):
 
 
 @torch.library.register_fake("mok::all_gather_top_experts")
-def _(top_experts, all_gather_top_experts_buffer, all_gather_top_experts_buffer_multicast_ptr, rank, chunk_bytes):
+def _(top_experts, all_gather_top_experts_buffer, all_gather_top_experts_buffer_multicast_ptr, rank, chunk_bytes,
+      peer_buffer_ptrs=None):
     return None
 
 

@@ -68,8 +68,8 @@ def lib() -> ctypes.CDLL:
         L.mok_schedule_static.restype = c_int
         L.mok_all_gather_top_experts.argtypes = [c_void_p, c_int64, POINTER(c_uint64), c_int, c_int, c_void_p]
         L.mok_barrier_all.argtypes = [c_void_p, POINTER(c_uint64), c_int, c_void_p, c_void_p, c_int, c_void_p]
-        L.mok_fwd_epilogue.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_void_p]
-        L.mok_bwd_epilogue.argtypes = [c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_void_p]
+        L.mok_fwd_epilogue.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_void_p, c_void_p]
+        L.mok_bwd_epilogue.argtypes = [c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_void_p, c_void_p]
         L.mok_mxfp8_quantize.argtypes = [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]
         for name in ("mok_moe_forward_bf16", "mok_moe_recompute_bf16", "mok_moe_backward_bf16",
                      "mok_moe_forward_mxfp8", "mok_moe_recompute_mxfp8", "mok_moe_backward_mxfp8"):

@@ -10,7 +10,7 @@ address); kernels report problems through `mok.ops.check_status()` instead of tr
 from __future__ import annotations
 
 import math
-from dataclasses import dataclass
+from dataclasses import dataclass, field
 from typing import Any
 
 import torch
@@ -64,7 +64,7 @@ class MoKForwardContext:               # reference :42-50
 
 
 @dataclass(slots=True)
-class MoKWorkspace:                    # reference :53-88 (same fields, same order)
+class MoKWorkspace:                    # reference :53-88 (same fields, same order; one more at the end)
     group_name: str
     ep_rank: int
     ep_size: int
@@ -99,6 +99,9 @@ class MoKWorkspace:                    # reference :53-88 (same fields, same ord
     barrier_buffer_ptrs: list[int]
     barrier_buffer_multicast_ptr: int
     barrier_target: torch.Tensor                      # (1,) int32
+    # every rank's address of the route gather buffer (unicast all-gather; the reference reaches peers through the
+    # multicast address alone and has no such field)
+    all_gather_top_experts_buffer_ptrs: list[int] = field(default_factory=list)
 
 
 _WORKSPACE_CACHE: dict[tuple[str, int, int, int, int, int], MoKWorkspace] = {}
@@ -193,7 +196,7 @@ def create_workspace(config: MoKConfig, group: dist.ProcessGroup, *, device: tor
     ag_buffer, ag_handle, ag_ptrs = allocate(ep_size, num_local_tokens, topk, dtype=torch.int32)
     barrier_buffer, barrier_handle, barrier_ptrs = allocate(1, dtype=torch.int32, zero=True)
     barrier_target = torch.zeros(1, dtype=torch.int32, device=device)
-    _ops.register_all_gather_peers(ag_buffer, ag_ptrs)
+    _ops.register_all_gather_peers(ag_buffer, ag_ptrs)   # for callers of the five-argument op; dies with the buffer
 
     dist.barrier(group=group, async_op=True, device_ids=[index]).block_current_stream()
 
@@ -210,7 +213,7 @@ def create_workspace(config: MoKConfig, group: dist.ProcessGroup, *, device: tor
         all_gather_top_experts_buffer_multicast_ptr=multicast_or_local(ag_buffer, ag_handle),
         barrier_buffer=barrier_buffer, barrier_buffer_handle=barrier_handle, barrier_buffer_ptrs=barrier_ptrs,
         barrier_buffer_multicast_ptr=multicast_or_local(barrier_buffer, barrier_handle),
-        barrier_target=barrier_target,
+        barrier_target=barrier_target, all_gather_top_experts_buffer_ptrs=ag_ptrs,
     )
 
 
@@ -292,7 +295,8 @@ def build_schedule(workspace: MoKWorkspace, config: MoKConfig, top_experts: torc
 
     routes = top_experts if top_experts.dtype == torch.int32 else top_experts.to(torch.int32)
     all_gather_top_experts(routes, workspace.all_gather_top_experts_buffer,
-                           workspace.all_gather_top_experts_buffer_multicast_ptr, workspace.ep_rank, chunk)
+                           workspace.all_gather_top_experts_buffer_multicast_ptr, workspace.ep_rank, chunk,
+                           workspace.all_gather_top_experts_buffer_ptrs or None)
     _barrier(workspace)
     peer_rank, peer_token_idx, num_tokens, tokens_per_expert = schedule(
         workspace.all_gather_top_experts_buffer, num_local_experts, workspace.schedule_capacity, workspace.ep_rank)
@@ -401,11 +405,15 @@ def backward(config: MoKConfig, workspace: MoKWorkspace, schedule: MoKSchedule, 
              routed_gate_weights: torch.Tensor | tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor],
              routed_up_weights: torch.Tensor | tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor],
              routed_down_weights: torch.Tensor | tuple[torch.Tensor, torch.Tensor],
-             swiglu_limit: float | None = None) -> tuple[torch.Tensor, ...]:
+             swiglu_limit: float | None = None, *, router_grad_view: bool = False) -> tuple[torch.Tensor, ...]:
     """MoE backward (reference :652-780).
 
     Returns (d_x, d_router_weights, d_routed_gate_weights, d_routed_up_weights, d_routed_down_weights,
              d_shared_gate_weights, d_shared_up_weights, d_shared_down_weights).
+
+    The peers write this rank's router-weight gradients into `workspace.d_router_weight_buffer`.  By default a copy
+    is returned, as the reference does (:778, which marks the copy as removable); with `router_grad_view=True` the
+    buffer itself is returned and stays valid until the next `backward` on this workspace overwrites it.
     """
     validate_inputs(config, workspace, schedule, x, router_weights, grad_output)
     if not isinstance(forward_context, MoKForwardContext):
@@ -442,6 +450,6 @@ def backward(config: MoKConfig, workspace: MoKWorkspace, schedule: MoKSchedule, 
 
     _barrier(workspace)
     d_x = bwd_epilogue(d_x_shared, workspace.d_x_routed_buffer)
-    d_router_weights = workspace.d_router_weight_buffer.clone()
+    d_router_weights = workspace.d_router_weight_buffer if router_grad_view else workspace.d_router_weight_buffer.clone()
     return (d_x, d_router_weights, d_w_routed_gate, d_w_routed_up, d_w_routed_down,
             d_w_shared_gate, d_w_shared_up, d_w_shared_down)

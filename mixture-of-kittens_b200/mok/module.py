@@ -103,7 +103,8 @@ class MoKMoE(torch.nn.Module):
 
     def __init__(self, hidden_size: int, intermediate_size: int, num_experts: int, topk: int, *,
                  group: dist.ProcessGroup | None = None, config: F.MoKConfig | None = None, swiglu_limit: float | None = None,
-                 recompute: bool = False, mxfp8: bool = False, device=None, init_std: float = 0.02):
+                 recompute: bool = False, mxfp8: bool = False, device=None, init_std: float = 0.02,
+                 cache_quantized: bool = True):
         super().__init__()
         self.group = group or dist.group.WORLD
         ep = dist.get_world_size(self.group)
@@ -113,6 +114,7 @@ class MoKMoE(torch.nn.Module):
         self.config = config or F.MoKConfig()
         self.swiglu_limit, self.recompute, self.mxfp8 = swiglu_limit, recompute, mxfp8
         self._quantized = None
+        self.cache_quantized = cache_quantized
         e_loc = num_experts // ep
 
         def param(*shape, dtype=torch.bfloat16):
@@ -123,11 +125,20 @@ class MoKMoE(torch.nn.Module):
         self.w_routed_gate, self.w_routed_up = param(e_loc, intermediate_size, hidden_size), param(e_loc, intermediate_size, hidden_size)
         self.w_routed_down = param(e_loc, hidden_size, intermediate_size)
 
+    def invalidate_quantized(self) -> None:
+        """Drops the cached MXFP8 copies of the routed weights; the next forward quantizes again.  Call it after any
+        weight update the version counters cannot see: writes through `param.data` (fused or foreach optimizers that
+        hold flat buffers, ZeRO-style shards, `param.data.copy_`)."""
+        self._quantized = None
+
     def _quantized_weights(self):
-        """MXFP8 copies of the routed weights, rebuilt only after one of them changed (optimizer step, load_state_dict)."""
+        """MXFP8 copies of the routed weights, rebuilt only after one of them changed (optimizer step, load_state_dict).
+        The change is detected through the parameters' version counters, which in-place updates of the Parameter bump
+        and writes through `.data` do not: after those call `invalidate_quantized()`, or construct the module with
+        `cache_quantized=False` to quantize in every forward."""
         params = (self.w_routed_gate, self.w_routed_up, self.w_routed_down)
         key = tuple((p.data_ptr(), p._version) for p in params)
-        if self._quantized is None or self._quantized[0] != key:
+        if not self.cache_quantized or self._quantized is None or self._quantized[0] != key:
             with torch.no_grad():
                 self._quantized = (key, quantize_routed_weights(*params))
         return self._quantized[1]

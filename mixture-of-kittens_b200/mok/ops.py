@@ -16,13 +16,19 @@ from ._native import LayerArgs, check, check_status, lib, ptr, ptr_array, status
 
 SUPPORTED_EP_SIZES = (1, 2, 4, 8)
 
-# all_gather_top_experts keeps the reference signature (a multicast address, no pointer list).  The peers'
-# buffer addresses of a symmetric all-gather buffer are registered here by the workspace that owns it.
+# all_gather_top_experts keeps the reference signature (a multicast address, no pointer list) and takes the peers'
+# buffer addresses as an optional last argument; `mok.functional` passes the list its workspace carries.  Callers that
+# use the five-argument form register the list of their symmetric buffer here instead.  An entry lives exactly as long
+# as the buffer it was registered for: it is dropped when that tensor is freed, so a later allocation at the same
+# address can never inherit it.
 _ALL_GATHER_PEERS: dict[int, list[int]] = {}
 
 
 def register_all_gather_peers(buffer: torch.Tensor, peer_ptrs: list[int]) -> None:
-    _ALL_GATHER_PEERS[int(buffer.data_ptr())] = [int(p) for p in peer_ptrs]
+    import weakref
+    key = int(buffer.data_ptr())
+    _ALL_GATHER_PEERS[key] = [int(p) for p in peer_ptrs]
+    weakref.finalize(buffer, _ALL_GATHER_PEERS.pop, key, None)
 
 
 def unregister_all_gather_peers(buffer: torch.Tensor) -> None:
@@ -169,6 +175,7 @@ def all_gather_top_experts(
     all_gather_top_experts_buffer_multicast_ptr: int,
     rank: int,
     chunk_bytes: int,
+    peer_buffer_ptrs: list[int] | None = None,
 ) -> None:
     """Writes this rank's routes into slot `rank` of every EP rank's gather buffer.
 
@@ -178,6 +185,9 @@ def all_gather_top_experts(
         all_gather_top_experts_buffer_multicast_ptr: int (kept for interface compatibility; not dereferenced)
         rank:                                        int
         chunk_bytes:                                 int (kept for interface compatibility; validated only)
+        peer_buffer_ptrs:                            list[int] [ep_size] or None: every rank's address of the gather
+                                                     buffer (not in the reference signature; None looks the list up
+                                                     among those given to `register_all_gather_peers`)
     """
     _require(top_experts.is_cuda and top_experts.dtype == torch.int32 and top_experts.is_contiguous() and top_experts.ndim == 2,
              "top_experts must be contiguous CUDA int32 [num_local_tokens, topk]")
@@ -202,7 +212,10 @@ def all_gather_top_experts(
     if ep_size == 1:
         buf[0].copy_(top_experts)
         return
-    peers = _ALL_GATHER_PEERS.get(int(buf.data_ptr()))
+    peers = peer_buffer_ptrs if peer_buffer_ptrs is not None else _ALL_GATHER_PEERS.get(int(buf.data_ptr()))
+    if peers is not None:
+        _require(isinstance(peers, list) and all(type(p) is int and p > 0 for p in peers),
+                 "peer_buffer_ptrs must be a list of positive integers", TypeError)
     if peers is None or len(peers) != ep_size:
         raise RuntimeError("all_gather_top_experts_buffer is not a registered symmetric buffer "
                            "(create it with mok.functional.create_workspace or call ops.register_all_gather_peers)")
@@ -548,7 +561,8 @@ def dispatch_mlp_swiglu_combine_bwd_bf16(
 # ------------------------------------------------------------------------------------------------------------
 @torch.library.custom_op("mok::fwd_epilogue", mutates_args=())
 def fwd_epilogue(y_shared: torch.Tensor, combine_buffer: torch.Tensor, topk_weights: torch.Tensor) -> torch.Tensor:
-    """output[t] = bf16(y_shared[t] + sum_k topk_weights[t, k] * combine_buffer[t*topk + k]), k ascending, fp32 sum."""
+    """output[t] = bf16(y_shared[t] + sum_k topk_weights[t, k] * combine_buffer[t*topk + k]), k ascending, fp32 sum.
+    If the device status word of this GPU holds an error bit (see `check_status`) the output is all NaN."""
     _require(y_shared.ndim == 2, "y_shared must have shape (num_local_tokens, hidden_size)")
     T, H = y_shared.shape
     _require(T >= 512 and T % 256 == 0, "num_local_tokens must be at least 512 and divisible by 256")
@@ -564,13 +578,14 @@ def fwd_epilogue(y_shared: torch.Tensor, combine_buffer: torch.Tensor, topk_weig
              and topk_weights.is_contiguous(), "fwd_epilogue needs contiguous CUDA bfloat16 activations and float32 weights")
     out = torch.empty_like(y_shared)
     check(lib().mok_fwd_epilogue(ptr(y_shared), ptr(combine_buffer), ptr(topk_weights), ptr(out), T, H, topk,
-                                 stream_ptr(y_shared.device)), "fwd_epilogue")
+                                 ptr(status_word(y_shared.device)), stream_ptr(y_shared.device)), "fwd_epilogue")
     return out
 
 
 @torch.library.custom_op("mok::bwd_epilogue", mutates_args=())
 def bwd_epilogue(d_x_shared: torch.Tensor, d_x_routed_buffer: torch.Tensor) -> torch.Tensor:
-    """d_x[t] = bf16(d_x_shared[t] + sum_k d_x_routed_buffer[t*topk + k]), k ascending, fp32 sum."""
+    """d_x[t] = bf16(d_x_shared[t] + sum_k d_x_routed_buffer[t*topk + k]), k ascending, fp32 sum.
+    If the device status word of this GPU holds an error bit (see `check_status`) the output is all NaN."""
     _require(d_x_shared.ndim == 2, "d_x_shared must have shape (num_local_tokens, hidden_size)")
     T, H = d_x_shared.shape
     _require(T >= 512 and T % 256 == 0, "num_local_tokens must be at least 512 and divisible by 256")
@@ -584,7 +599,7 @@ def bwd_epilogue(d_x_shared: torch.Tensor, d_x_routed_buffer: torch.Tensor) -> t
              "bwd_epilogue needs contiguous CUDA bfloat16 tensors")
     out = torch.empty_like(d_x_shared)
     check(lib().mok_bwd_epilogue(ptr(d_x_shared), ptr(d_x_routed_buffer), ptr(out), T, H, d_x_routed_buffer.shape[0] // T,
-                                 stream_ptr(d_x_shared.device)), "bwd_epilogue")
+                                 ptr(status_word(d_x_shared.device)), stream_ptr(d_x_shared.device)), "bwd_epilogue")
     return out
 
 

@@ -28,8 +28,8 @@ def test_entry_points_reject_bad_arguments_without_a_gpu():
     L = nat.lib()
     assert L.mok_schedule(None, 1, 512, 1, 1, 512, 0, None, None, None, None, None, None, None) == -1
     assert L.mok_mxfp8_quantize(None, 1, 128, 128, None, None, None, None, None) == -1
-    assert L.mok_fwd_epilogue(None, None, None, None, 512, 256, 1, None) == -1
-    assert L.mok_bwd_epilogue(None, None, None, 512, 256, 1, None) == -1
+    assert L.mok_fwd_epilogue(None, None, None, None, 512, 256, 1, None, None) == -1
+    assert L.mok_bwd_epilogue(None, None, None, 512, 256, 1, None, None) == -1
     assert L.mok_barrier_all(None, None, 2, None, None, 0, None) == -1
     assert L.mok_grouped_gemm_bf16(None, None, None, None, None, 1, 256, 256, 64, 0, None, None) == -1
     args = nat.LayerArgs()

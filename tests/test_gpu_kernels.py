@@ -85,9 +85,17 @@ def test_schedule_overflow_sets_status_instead_of_trapping(dev):
     out = mok.ops.schedule(topk_all.to(dev), 1, T * K, 0)        # 1024 routes into a capacity of 512
     torch.cuda.synchronize()
     assert int(out[2].item()) == 1024
+    # while the word holds an error bit the epilogues hand out NaN instead of sums over slots that may be stale
+    shared = torch.ones(T, 256, device=dev, dtype=torch.bfloat16)
+    routed = torch.ones(T * K, 256, device=dev, dtype=torch.bfloat16)
+    w = torch.ones(T, K, device=dev)
+    assert torch.isnan(mok.ops.fwd_epilogue(shared, routed, w).float()).all()
+    assert torch.isnan(mok.ops.bwd_epilogue(shared, routed).float()).all()
     with pytest.raises(RuntimeError, match="schedule overflow"):
         mok.ops.check_status(dev)
     mok.ops.check_status(dev)   # the word was reset
+    assert torch.all(mok.ops.fwd_epilogue(shared, routed, w) == 2.0)
+    assert torch.all(mok.ops.bwd_epilogue(shared, routed) == 2.0)
 
 
 def test_schedule_rejects_bad_arguments(dev):

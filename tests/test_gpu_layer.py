@@ -75,6 +75,54 @@ def test_layer_fwd_bwd_matches_oracle(dist_ctx, case):
     _compare(ref, out, grads, name)
 
 
+SWEEP = [("topk-1", 4, 1), ("topk-6", 8, 6), ("local-experts-6", 6, 4), ("local-experts-12", 12, 4), ("local-experts-24", 24, 8),
+         ("local-experts-32", 32, 8)]
+
+
+@pytest.mark.parametrize("name,E,K", SWEEP, ids=[c[0] for c in SWEEP])
+def test_topk_values_and_local_expert_counts(dist_ctx, name, E, K):
+    """top-k values and local-expert counts of the reference's end-to-end sweeps (tests/test_misc.py:1852,1883), with
+    its small ring (minibatch 256, macrobatch 512: every case runs several windows and the backward replay)."""
+    import mok
+    H, I, T = 512, 256, 512
+    # capacity 3 x the routes: with 32 experts the padding to 256 rows per expert alone can double the row count
+    config = mok.functional.MoKConfig(minibatch_size=256, macrobatch_size=512, schedule_capacity_multiplier=3.0)
+    inp = O.make_rank_inputs(0, E, E, K, T, H, I)
+    ref = O.moe_layer_oracle([inp])[0]
+    out, grads = _run(dist_ctx, inp, E, config)
+    _compare(ref, out, grads, name)
+
+
+def test_workspace_cache_reuse_and_isolation(dist_ctx):
+    """`get_workspace` returns the cached object for the same (group, device, sizes, capacity factor), a new one for a
+    larger capacity multiplier or another process group, and `create_workspace` never touches the cache (reference
+    tests/test_misc.py:577-645)."""
+    import math
+    import torch.distributed as dist
+    import mok
+    F = mok.functional
+    _, world, dev = dist_ctx
+    F.clear_workspace_cache()
+    duplicate_world = dist.new_group(ranks=list(range(world)))
+    kwargs = dict(device=dev, num_local_tokens=512, hidden_size=256, topk=1)
+    default_config = F.MoKConfig(minibatch_size=256, macrobatch_size=512)
+    larger_config = F.MoKConfig(minibatch_size=256, macrobatch_size=512, schedule_capacity_multiplier=2.5)
+    try:
+        created = F.create_workspace(default_config, dist.group.WORLD, **kwargs)
+        default = F.get_workspace(default_config, dist.group.WORLD, **kwargs)
+        reused = F.get_workspace(default_config, dist.group.WORLD, **kwargs)
+        larger = F.get_workspace(larger_config, dist.group.WORLD, **kwargs)
+        duplicate = F.get_workspace(default_config, duplicate_world, **kwargs)
+        assert created is not default and reused is default and larger is not default and duplicate is not default
+        assert default.schedule_capacity == 512 * max(2, math.ceil(world * 0.5))
+        assert larger.schedule_capacity == 512 * max(2, math.ceil(world * 2.5))
+        assert duplicate.group_name == duplicate_world.group_name != default.group_name
+        assert created.x_buffer.data_ptr() != default.x_buffer.data_ptr()
+    finally:
+        F.clear_workspace_cache()
+        dist.destroy_process_group(duplicate_world)
+
+
 def test_cpu_plumbing_configuration_against_fp32_math(dist_ctx):
     """The small configuration of the acceptance list (2048 tokens, hidden 512, 8 experts of intermediate 1024, top-2,
     weights ~ N(0, 0.02), seed 0) against plain fp32 math of the same layer: rel-L2 <= 1e-2 for outputs and gradients."""

@@ -134,6 +134,30 @@ def test_mxfp8_layer_fwd_bwd(dist_ctx, case):
     assert not problems, name + " | " + " ; ".join(problems)
 
 
+MX_SWEEP = [("topk-1", 4, 1), ("topk-6", 8, 6), ("local-experts-12", 12, 8), ("local-experts-24", 24, 8)]
+
+
+@pytest.mark.parametrize("name,E,K", MX_SWEEP, ids=[c[0] for c in MX_SWEEP])
+def test_mxfp8_topk_values_and_local_expert_counts(dist_ctx, name, E, K):
+    """The reference's top-k and local-expert sweeps in MXFP8 (tests/test_misc.py:1852,1883), on its small ring."""
+    import mok
+    H, I, T = 512, 256, 512
+    # capacity 3 x the routes: with 32 experts the padding to 256 rows per expert alone can double the row count
+    config = mok.functional.MoKConfig(minibatch_size=256, macrobatch_size=512, schedule_capacity_multiplier=3.0)
+    inp = O.make_rank_inputs(0, E, E, K, T, H, I)
+    emu = O.moe_layer_oracle([inp], mxfp8=True)[0]
+    ref = O.moe_layer_oracle([inp])[0]
+    out, grads = _run_mxfp8_layer(dist_ctx, inp, E, config)
+    problems = []
+    for field, got in (("output", out),) + tuple(zip(FIELDS, grads)):
+        g = got.float().cpu()
+        _, _, l2, _ = O.error_stats(getattr(emu, field).float(), g)
+        mx, l1, _, cos = O.error_stats(getattr(ref, field).float(), g)
+        if not (l2 <= 3e-2 and mx <= 1.0 and l1 <= 0.1 and cos >= 0.996):
+            problems.append(f"{field}: vs-emulation l2 {l2:.3e}; vs-bf16 max {mx:.3e} l1 {l1:.3e} cos {cos:.5f}")
+    assert not problems, name + " | " + " ; ".join(problems)
+
+
 def test_mxfp8_layer_bitwise_repeat(dist_ctx):
     import mok
     E, H, I, K, T = 8, 256, 256, 2, 1024
