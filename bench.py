@@ -243,19 +243,25 @@ def make_weights(w, e_loc: int, rank: int, dev):
 # ------------------------------------------------------------------------------------------------------------
 # GPU arm: single launches of the dominant kernels
 # ------------------------------------------------------------------------------------------------------------
-def _time_launches(fn, name, reps=5):
+def _time_forms(named_fns, reps=5):
+    """Average duration of single launches of each form, timed with one CUDA-event pair per launch and the forms taken
+    in turn (a, b, c, a, b, c, ...): under the power cap the SM clock sinks within milliseconds of sustained load, so
+    forms timed one after the other in blocks would be measured at different clocks; in turn they share the same state."""
     import torch
     from mok import _native as nat
-    for _ in range(2):
-        nat.check(fn(), name)
-    ev = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
+    for name, fn in named_fns:
+        for _ in range(2):
+            nat.check(fn(), name)
+    events = {name: [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(reps)]
+              for name, _ in named_fns}
     torch.cuda.synchronize()
-    ev[0].record()
-    for _ in range(reps):
-        fn()
-    ev[1].record()
+    for i in range(reps):
+        for name, fn in named_fns:
+            events[name][i][0].record()
+            fn()
+            events[name][i][1].record()
     torch.cuda.synchronize()
-    return ev[0].elapsed_time(ev[1]) / reps
+    return {name: sum(a.elapsed_time(b) for a, b in events[name]) / reps for name, _ in named_fns}
 
 
 def time_gemm_forms(dev, w, e_loc, sched, weights, rows_buf):
@@ -287,8 +293,7 @@ def time_gemm_forms(dev, w, e_loc, sched, weights, rows_buf):
                                         nat.ptr(st), nat.stream_ptr(dev))
     out = {}
     rows_done = min(valid_rows, rows_buf)
-    for name, fn in (("fwd_gate", fwd), ("dgrad_down", dgrad), ("wgrad_gate", wgrad)):
-        ms = _time_launches(fn, name)
+    for name, ms in _time_forms((("fwd_gate", fwd), ("dgrad_down", dgrad), ("wgrad_gate", wgrad))).items():
         out[name] = {"ms": ms, "tflops": 2.0 * rows_done * H * I / (ms * 1e-3) / 1e12}
     nat.check_status(dev)
     return out, rows_done
@@ -323,8 +328,7 @@ def time_gemm_forms_mxfp8(dev, w, e_loc, sched, qg, rows_buf):
                                          rows_buf, I, H, nat.ptr(st), nat.stream_ptr(dev))
     out = {}
     rows_done = min(valid_rows, rows_buf)
-    for name, fn in (("fwd_gate", fwd), ("wgrad_gate", wgrad)):
-        ms = _time_launches(fn, name)
+    for name, ms in _time_forms((("fwd_gate", fwd), ("wgrad_gate", wgrad))).items():
         out[name] = {"ms": ms, "tflops": 2.0 * rows_done * H * I / (ms * 1e-3) / 1e12}
     nat.check_status(dev)
     return out, rows_done

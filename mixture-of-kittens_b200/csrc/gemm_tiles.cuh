@@ -33,6 +33,9 @@ struct KernelParams {
     int n_tiles_per_expert;   // MXFP8 rows form: N / 128, scale row tiles of one expert's weight
     bf16* D0;
     bf16* D1;
+    bf16* D2;                 // bf16 kernel, fused gate / up form: hidden = silu(gate) * up (D0 = gate, D1 = up)
+    int clamp;                // fused gate / up form: SwiGLU clamp on
+    float limit;
     int out_f32;              // bf16 kernel: D0 is an fp32 array (router logits and router weight gradient)
     long long ldd;
     long long d_expert_stride;

@@ -17,7 +17,13 @@
 //   rows / B [E,K,N]   D[r,:] = sum_s A_s[r,:] B_s[e]  dgrad down; dgrad gate+up (2 sets) (B MN-major)
 //   wgrad              D[e] (+)= A[rows_e,:]^T B[rows_e,:], K = rows of expert e          (A, B MN-major)
 // Every output element has exactly one writer and a fixed K order, so results are run-to-run identical.
+//
+// Fused gate / up form (forward): one tile holds 128 gate columns and the same 128 up columns (CTA 0 stages the gate
+// weights, CTA 1 the up weights, so accumulator columns [0, 128) are gate and [128, 256) up); the epilogue rounds both
+// to bf16, stores them (backward needs them) and forms hidden = silu(gate) * up from the rounded values, which is
+// exactly what a separate SwiGLU pass over the stored gate / up would compute, without reading them back.
 #include "gemm_tiles.cuh"
+#include "swiglu_math.cuh"
 
 namespace mok {
 namespace {
@@ -47,13 +53,14 @@ struct SharedLayout {
 };
 
 
-template <int MODE, bool B_MN>
+template <int MODE, bool B_MN, bool FUSED>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__ CUtensorMap tmB0,
                     const __grid_constant__ CUtensorMap tmA1, const __grid_constant__ CUtensorMap tmB1,
                     const KernelParams p) {
     constexpr bool A_MN = (MODE == MODE_WGRAD);
     static_assert(MODE == MODE_ROWS || B_MN, "the weight-gradient form reads both operands MN-major");
+    static_assert(!FUSED || (MODE == MODE_ROWS && !B_MN), "the fused gate / up form is a forward rows form");
 
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -132,8 +139,9 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_const
                         const int kset = kb >= p.k_blocks ? 1 : 0;
                         const int kk = (kb - kset * p.k_blocks) * BK;
                         tma_load_4d_pair(a_dst, kset ? &tmA1 : &tmA0, full, kk, tile.row0 - p.row_begin + cta_rank * BM_CTA, 0, 0);
-                        const CUtensorMap* bmap = (kset || tile.set) ? &tmB1 : &tmB0;
-                        const int n_cta = tile.n0 + cta_rank * BN_CTA;
+                        // fused gate / up: CTA 0 stages the tile's 128 gate rows, CTA 1 the same 128 up rows
+                        const CUtensorMap* bmap = FUSED ? (cta_rank ? &tmB1 : &tmB0) : ((kset || tile.set) ? &tmB1 : &tmB0);
+                        const int n_cta = FUSED ? tile.n0 / 2 : tile.n0 + cta_rank * BN_CTA;
                         if (!B_MN) {
                             tma_load_4d_pair(b_dst, bmap, full, kk, n_cta, tile.expert, 0);
                         } else {
@@ -211,7 +219,9 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_const
             if (!ok) break;
             tc_fence_after_sync();
             bf16* out;
-            if (MODE == MODE_ROWS)
+            if (FUSED)
+                out = p.D0;   // the fused form addresses its three outputs itself
+            else if (MODE == MODE_ROWS)
                 out = (tile.set ? p.D1 : p.D0) + static_cast<long long>(tile.row0 - p.row_begin + row_in_tile) * p.ldd + tile.n0;
             else
                 out = p.D0 + static_cast<long long>(tile.expert) * p.d_expert_stride +
@@ -219,6 +229,42 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_const
             const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * BN;
             uint8_t* patch = smem_gen + SharedLayout::kEpilogue + quarter * kEpiWarpBytes;
             bf16* warp_out = out - static_cast<long long>(lane) * p.ldd;   // row of lane 0
+            if (FUSED) {
+                // row of lane 0 at the tile's first gate / up / hidden column
+                const long long first = static_cast<long long>(tile.row0 - p.row_begin + cta_rank * BM_CTA + quarter * 32) * p.ldd +
+                                        tile.n0 / 2;
+#pragma unroll 1
+                for (int c = 0; c < 2; ++c) {   // 64 gate columns and the same 64 up columns per round
+                    uint4 gate[8], up[8], hid[8];
+                    {
+                        uint32_t v0[32], v1[32];
+                        tmem_ld_32x32(taddr + c * 64, v0);
+                        tmem_ld_32x32(taddr + c * 64 + 32, v1);
+                        tmem_ld_wait();
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) { gate[i] = pack8_bf16(&v0[8 * i]); gate[4 + i] = pack8_bf16(&v1[8 * i]); }
+                        tmem_ld_32x32(taddr + BN_CTA + c * 64, v0);
+                        tmem_ld_32x32(taddr + BN_CTA + c * 64 + 32, v1);
+                        tmem_ld_wait();
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) { up[i] = pack8_bf16(&v0[8 * i]); up[4 + i] = pack8_bf16(&v1[8 * i]); }
+                    }
+                    if (p.clamp) {
+#pragma unroll
+                        for (int i = 0; i < 8; ++i)
+                            hid[i] = make_uint4(swiglu_pair<true>(gate[i].x, up[i].x, p.limit), swiglu_pair<true>(gate[i].y, up[i].y, p.limit),
+                                                swiglu_pair<true>(gate[i].z, up[i].z, p.limit), swiglu_pair<true>(gate[i].w, up[i].w, p.limit));
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < 8; ++i)
+                            hid[i] = make_uint4(swiglu_pair<false>(gate[i].x, up[i].x, 0.f), swiglu_pair<false>(gate[i].y, up[i].y, 0.f),
+                                                swiglu_pair<false>(gate[i].z, up[i].z, 0.f), swiglu_pair<false>(gate[i].w, up[i].w, 0.f));
+                    }
+                    epilogue_store_packed_64cols(patch, gate, p.D0 + first + c * 64, p.ldd, lane);
+                    epilogue_store_packed_64cols(patch, up, p.D1 + first + c * 64, p.ldd, lane);
+                    epilogue_store_packed_64cols(patch, hid, p.D2 + first + c * 64, p.ldd, lane);
+                }
+            } else
 #pragma unroll 1
             for (int c = 0; c < BN / 64; ++c) {
                 uint32_t v0[32], v1[32];
@@ -272,11 +318,11 @@ size_t smem_bytes(int num_experts) {
     return 1024 + SharedLayout::kCum + 4 * (static_cast<size_t>(num_experts) + 2);
 }
 
-template <int MODE, bool B_MN>
+template <int MODE, bool B_MN, bool FUSED = false>
 int launch(const CUtensorMap& a0, const CUtensorMap& b0, const CUtensorMap& a1, const CUtensorMap& b1,
            const KernelParams& kp, int max_tiles, cudaStream_t stream) {
     static int resident_pairs[16] = {0};
-    return launch_pairs(grouped_gemm_kernel<MODE, B_MN>, "grouped_gemm_kernel", resident_pairs, smem_bytes(kp.num_experts),
+    return launch_pairs(grouped_gemm_kernel<MODE, B_MN, FUSED>, "grouped_gemm_kernel", resident_pairs, smem_bytes(kp.num_experts),
                         max_tiles, stream, a0, b0, a1, b1, kp);
 }
 
@@ -309,6 +355,28 @@ int launch_rows_gemm(const GemmProblem& pb, const void* A, int K, const void* B0
     const int max_tiles = (window / BM) * kp.n_blocks * n_sets;
     return b_is_kn ? launch<MODE_ROWS, true>(a0, b0, a0, b1, kp, max_tiles, stream)
                    : launch<MODE_ROWS, false>(a0, b0, a0, b1, kp, max_tiles, stream);
+}
+
+int launch_gate_up_fused(const GemmProblem& pb, const void* A, int K, const void* Wg, const void* Wu, void* gate, void* up,
+                         void* hidden, int N, bool has_limit, float limit, cudaStream_t stream) {
+    int rc = check_problem(pb);
+    if (rc != MOK_OK) return rc;
+    if (K <= 0 || N <= 0 || K % BK != 0 || N % BN_CTA != 0 || !Wg || !Wu || !gate || !up || !hidden) return MOK_ERR_INVALID_ARGUMENT;
+    CUtensorMap a0, b0, b1;
+    if ((rc = make_map(&a0, A, K, pb.buffer_rows, 1, BK, BM_CTA)) != MOK_OK) return rc;
+    if ((rc = make_map(&b0, Wg, K, N, pb.num_experts, BK, BN_CTA)) != MOK_OK) return rc;
+    if ((rc = make_map(&b1, Wu, K, N, pb.num_experts, BK, BN_CTA)) != MOK_OK) return rc;
+    KernelParams kp = base_params(pb);
+    kp.n_blocks = N / BN_CTA;   // one tile per 128 gate columns + the same 128 up columns
+    kp.k_blocks = K / BK;
+    kp.D0 = static_cast<bf16*>(gate);
+    kp.D1 = static_cast<bf16*>(up);
+    kp.D2 = static_cast<bf16*>(hidden);
+    kp.clamp = has_limit ? 1 : 0;
+    kp.limit = limit;
+    kp.ldd = N;
+    const int window = pb.row_end - pb.row_begin;
+    return launch<MODE_ROWS, false, true>(a0, b0, a0, b1, kp, (window / BM) * kp.n_blocks, stream);
 }
 
 int launch_rows_gemm_dual(const GemmProblem& pb, const void* A0, const void* A1, int K, const void* B0, const void* B1,

@@ -27,6 +27,11 @@ struct GemmProblem {
 int launch_rows_gemm(const GemmProblem& pb, const void* A, int K, const void* B0, const void* B1, void* D0, void* D1,
                      int N, bool b_is_kn, cudaStream_t stream);
 
+// Forward gate and up projections with the SwiGLU in the epilogue: gate = A * Wg[e]^T, up = A * Wu[e]^T (both stored as
+// bf16 [rows, N]) and hidden = silu(gate) * up computed from the stored (rounded) values, optionally clamped.
+int launch_gate_up_fused(const GemmProblem& pb, const void* A, int K, const void* Wg, const void* Wu, void* gate, void* up,
+                         void* hidden, int N, bool has_limit, float limit, cudaStream_t stream);
+
 // D[row, :] = A0[row, :K] * B0[e] + A1[row, :K] * B1[e] with B_s stored [E, K, N] (gate+up input gradient).
 int launch_rows_gemm_dual(const GemmProblem& pb, const void* A0, const void* A1, int K, const void* B0, const void* B1,
                           void* D, int N, cudaStream_t stream);

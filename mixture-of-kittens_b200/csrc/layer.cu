@@ -240,6 +240,13 @@ bool fused_epilogue_enabled() {
     return !(v != nullptr && v[0] == '1');
 }
 
+// MOK_NO_FUSED_SWIGLU=1: the bf16 gate / up GEMM writes gate and up only and a separate SwiGLU kernel reads them back to
+// form hidden, instead of forming it in the GEMM's own epilogue (same bytes either way)
+bool fused_swiglu_enabled() {
+    const char* v = getenv("MOK_NO_FUSED_SWIGLU");
+    return !(v != nullptr && v[0] == '1');
+}
+
 // MOK_NO_WGRAD_TRIM=1 lets the weight-gradient GEMMs run over the padding rows too (for measurements; same results)
 bool wgrad_trim_enabled() {
     const char* v = getenv("MOK_NO_WGRAD_TRIM");
@@ -275,6 +282,10 @@ int dispatch_x(const mok_layer_args* a, const Span& s, int ctas, cudaStream_t st
 
 int gate_up_hidden(const mok_layer_args* a, const Span& s, cudaStream_t st) {
     const int H = a->hidden, I = a->intermediate;
+    if (fused_swiglu_enabled())
+        return launch_gate_up_fused(routed_problem(a, s), rows_bf16(a->x_routed, s, H), H, a->w_routed_gate, a->w_routed_up,
+                                    rows_bf16(a->gate_routed, s, I), rows_bf16(a->up_routed, s, I),
+                                    rows_bf16(a->hidden_routed, s, I), I, a->has_swiglu_limit != 0, a->swiglu_limit, st);
     MOK_TRY(launch_rows_gemm(routed_problem(a, s), rows_bf16(a->x_routed, s, H), H, a->w_routed_gate, a->w_routed_up,
                              rows_bf16(a->gate_routed, s, I), rows_bf16(a->up_routed, s, I), I, false, st));
     MOK_TRY(launch_swiglu_fwd(rows_bf16(a->gate_routed, s, I), rows_bf16(a->up_routed, s, I), rows_bf16(a->hidden_routed, s, I),
@@ -284,6 +295,9 @@ int gate_up_hidden(const mok_layer_args* a, const Span& s, cudaStream_t st) {
 
 int shared_up_to_hidden(const mok_layer_args* a, cudaStream_t s) {
     const GemmProblem p = shared_problem(a);
+    if (fused_swiglu_enabled())
+        return launch_gate_up_fused(p, a->x_local, a->hidden, a->w_shared_gate, a->w_shared_up, a->gate_shared, a->up_shared,
+                                    a->hidden_shared, a->intermediate, a->has_swiglu_limit != 0, a->swiglu_limit, s);
     MOK_TRY(launch_rows_gemm(p, a->x_local, a->hidden, a->w_shared_gate, a->w_shared_up, a->gate_shared, a->up_shared,
                              a->intermediate, false, s));
     MOK_TRY(launch_swiglu_fwd(a->gate_shared, a->up_shared, a->hidden_shared, nullptr, a->num_local_tokens, 0,

@@ -297,3 +297,22 @@ def test_degenerate_routing_all_tokens_pick_first_experts(dist_ctx):
     # experts 8..15 received nothing: their weight gradients are exactly zero
     for g in grads[2:5]:
         assert torch.count_nonzero(g[K:]) == 0
+
+
+@pytest.mark.parametrize("limit", [None, 1.0])
+def test_swiglu_in_the_gemm_epilogue_equals_the_separate_kernel(dist_ctx, monkeypatch, limit):
+    """By default the forward gate / up GEMM forms hidden = silu(gate) * up in its epilogue from the bf16-rounded gate
+    and up it stores; with MOK_NO_FUSED_SWIGLU=1 a separate kernel reads gate and up back.  Same arithmetic on the same
+    values, so every output and gradient is bitwise equal (routed and shared expert, ring of two windows)."""
+    import mok
+    E, H, I, K, T = 8, 256, 768, 2, 1024
+    config = mok.functional.MoKConfig(minibatch_size=256, macrobatch_size=2048)
+    inp = O.make_rank_inputs(0, E, E, K, T, H, I)
+    monkeypatch.setenv("MOK_NO_FUSED_SWIGLU", "1")
+    out_a, grads_a = _run(dist_ctx, inp, E, config, limit)
+    monkeypatch.delenv("MOK_NO_FUSED_SWIGLU")
+    out_b, grads_b = _run(dist_ctx, inp, E, config, limit, recompute=True)
+    _compare(O.moe_layer_oracle([inp], swiglu_limit=limit)[0], out_b, grads_b, "fused swiglu")
+    assert torch.equal(out_a, out_b)
+    for name, a, b in zip(FIELDS, grads_a, grads_b):
+        assert torch.equal(a, b), name
