@@ -93,6 +93,40 @@ int mok_schedule_static(const int32_t* topk_all, int ep_size, int num_local_toke
                         int32_t* tokens_per_expert, uint32_t* status, mok_stream_t stream);
 
 /*
+ * Extends a finished schedule for de-duplicated dispatch: a token that several local experts use is pulled from its
+ * source rank once and fanned out locally, instead of once per schedule row as the reference's dispatch does
+ * (csrc/megakernel/dispatch_combine.cuh:74-77 pulls per row; the reference has no counterpart of this call).
+ *   row_source     int32 [cap]            number of the row's token among the staged tokens, -1 on padding rows
+ *   unique_peer    int32 [max_unique]     source rank of staged token u (numbered in the order of their first row)
+ *   unique_token   int32 [max_unique]     its token index on that rank
+ *   unique_before  int32 [cap / 256 + 1]  staged tokens whose first row lies below row 256 * i
+ *   num_unique     int32 [1]
+ *   scratch        mok_schedule_dedup_scratch_bytes() bytes
+ * max_unique >= min(cap, ep_size * num_local_tokens) always suffices.
+ */
+int64_t mok_schedule_dedup_scratch_bytes(int ep_size, int num_local_tokens, int topk, int schedule_capacity);
+int mok_schedule_dedup(const int32_t* topk_all, int ep_size, int num_local_tokens, int topk, int num_local_experts,
+                       int schedule_capacity, int rank, const int32_t* peer_rank, const int32_t* peer_token_idx,
+                       const int32_t* num_tokens, int32_t* row_source, int32_t* unique_peer, int32_t* unique_token,
+                       int32_t* unique_before, int32_t* num_unique, int max_unique, int32_t* scratch, mok_stream_t stream);
+
+/*
+ * The two steps of a de-duplicated dispatch, exposed for tests and for hosts that drive the pieces themselves.
+ * mok_stage_unique_rows: staged[u, :] = src_ptrs[unique_peer[u]][unique_token[u], :] for the staged tokens first used
+ * by schedule rows [from_row, min(to_row, *num_tokens)) (multiples of 256), except this rank's own tokens.
+ * mok_dispatch_rows_staged: mok_dispatch_rows, with the rows of other ranks' tokens read from `staged`.
+ */
+int mok_stage_unique_rows(const uint64_t* src_ptrs, int ep_size, int rank, const int32_t* unique_peer,
+                          const int32_t* unique_token, const int32_t* unique_before, const int32_t* num_tokens,
+                          int from_row, int to_row, int num_local_tokens, int hidden, void* staged, int staged_rows,
+                          int num_ctas, uint32_t* status, mok_stream_t stream);
+int mok_dispatch_rows_staged(const uint64_t* src_ptrs, const uint64_t* weight_ptrs, int ep_size, int rank,
+                             const int32_t* peer_rank, const int32_t* peer_token_idx, const int32_t* num_tokens,
+                             const int32_t* row_source, const void* staged, int staged_rows, int row_begin, int row_end,
+                             int topk, int num_local_tokens, int hidden, void* dst, float* row_weight, int num_ctas,
+                             uint32_t* status, mok_stream_t stream);
+
+/*
  * Copies this rank's int32 routes [T*K] into slot `rank` of the [ep, T, K] buffer of every peer.
  * Replaces: all_gather_top_experts_kernel, csrc/utils.cuh:191-227 (op mok/ops.py:6-61).  Peers are
  * addressed one by one through `peer_buffers` (unicast stores); no multicast object is needed.
@@ -225,6 +259,13 @@ typedef struct mok_layer_args {
     void *d_y_fp8_t, *d_y_sc_t;                     /* [H,MB] scratch */
     void *d_gate_fp8, *d_gate_sc, *d_up_fp8, *d_up_sc;              /* [MB,I] backward out */
     void *d_gate_fp8_t, *d_gate_sc_t, *d_up_fp8_t, *d_up_sc_t;      /* [I,MB] scratch */
+    /* De-duplicated dispatch (all NULL / 0 = every schedule row pulls its token itself).  The four index arrays are
+     * mok_schedule_dedup outputs; the staging buffers are caller-provided scratch of staged_rows x H bf16: staged_x for
+     * the forward / recompute calls and for the backward replay of later macrobatches, staged_d_y for the backward. */
+    const int32_t *row_source, *unique_peer, *unique_token, *unique_before;
+    void *staged_x, *staged_d_y;
+    int staged_rows;
+    int reserved1;
 } mok_layer_args;
 
 /*

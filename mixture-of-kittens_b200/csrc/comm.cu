@@ -68,14 +68,50 @@ __device__ __forceinline__ uint4 scale_vec(uint4 a, float w) {
     return make_uint4(scale_pair(a.x, w), scale_pair(a.y, w), scale_pair(a.z, w), scale_pair(a.w, w));
 }
 
+// ---- staging of de-duplicated tokens -----------------------------------------------------------------------
+// One warp per staged token of the range first used by rows [from_row, min(to_row, *num_tokens)).
+__global__ void __launch_bounds__(256) stage_tokens_kernel(PeerTable src, const int* __restrict__ unique_peer,
+                                                            const int* __restrict__ unique_token,
+                                                            const int* __restrict__ unique_before,
+                                                            const int* __restrict__ num_tokens, int from_row, int to_row, int ep,
+                                                            int self_rank, int tokens_per_rank, int hidden, int staged_rows,
+                                                            uint4* __restrict__ staged, uint32_t* status) {
+    const int hi_row = min(to_row, *num_tokens);
+    if (hi_row <= from_row) return;
+    const int u_begin = unique_before[from_row / 256];
+    const int u_end = min(unique_before[hi_row / 256], staged_rows);
+    const int vec_per_row = hidden / 8;
+    const int warps = (gridDim.x * blockDim.x) >> 5;
+    const int lane = threadIdx.x & 31;
+    for (int u = u_begin + ((blockIdx.x * blockDim.x + threadIdx.x) >> 5); u < u_end; u += warps) {
+        const int peer = unique_peer[u];
+        const int token = unique_token[u];
+        if (peer == self_rank) continue;   // rows of local tokens read the local input directly
+        if (peer < 0 || peer >= ep || token < 0 || token >= tokens_per_rank) {
+            if (lane == 0 && status != nullptr) atomicOr(status, (uint32_t)MOK_STATUS_BAD_SCHEDULE_ENTRY);
+            continue;
+        }
+        const uint4* in = reinterpret_cast<const uint4*>(src.ptr[peer]) + static_cast<size_t>(token) * vec_per_row;
+        uint4* out = staged + static_cast<size_t>(u) * vec_per_row;
+        int v = lane;
+        for (; v + 96 < vec_per_row; v += 128) {   // four independent 16-byte loads in flight per lane
+            const uint4 a = in[v], b = in[v + 32], c = in[v + 64], d = in[v + 96];
+            out[v] = a; out[v + 32] = b; out[v + 64] = c; out[v + 96] = d;
+        }
+        for (; v < vec_per_row; v += 32) out[v] = in[v];
+    }
+}
+
 // ---- dispatch ----------------------------------------------------------------------------------------------
 // One warp per schedule row: dst[row - row_begin] = src_peer[token] (optionally * router weight, rounded to bf16).
+// With row_source != nullptr the rows of other ranks' tokens are read from the local staging buffer instead.
 template <bool SCALE>
 __global__ void __launch_bounds__(256) dispatch_kernel(PeerTable src, PeerTable weights, const int* __restrict__ peer_rank,
                                                         const int* __restrict__ peer_token, const int* __restrict__ num_tokens,
                                                         int row_begin, int row_end, int ep, int topk, int tokens_per_rank,
                                                         int hidden, uint4* __restrict__ dst, float* __restrict__ row_weight,
-                                                        uint32_t* status) {
+                                                        uint32_t* status, const int* __restrict__ row_source,
+                                                        const uint4* __restrict__ staged, int staged_rows, int self_rank) {
     const int hi = min(row_end, *num_tokens);
     const int vec_per_row = hidden / 8;
     const int warps = (gridDim.x * blockDim.x) >> 5;
@@ -95,6 +131,16 @@ __global__ void __launch_bounds__(256) dispatch_kernel(PeerTable src, PeerTable 
             continue;
         }
         const uint4* in = reinterpret_cast<const uint4*>(src.ptr[peer]) + static_cast<size_t>(route / topk) * vec_per_row;
+        if (row_source != nullptr && peer != self_rank) {
+            const int u = row_source[row];
+            if (u < 0 || u >= staged_rows) {
+                if (lane == 0 && status != nullptr) atomicOr(status, (uint32_t)MOK_STATUS_BAD_SCHEDULE_ENTRY);
+                for (int v = lane; v < vec_per_row; v += 32) out[v] = make_uint4(0, 0, 0, 0);
+                if (SCALE && lane == 0) row_weight[row - row_begin] = 0.0f;
+                continue;
+            }
+            in = staged + static_cast<size_t>(u) * vec_per_row;
+        }
         float w = 1.0f;
         if (SCALE) {
             w = reinterpret_cast<const float*>(weights.ptr[peer])[route];
@@ -155,22 +201,46 @@ int comm_grid(int rows, int num_ctas_hint) {
 
 }  // namespace
 
+int launch_stage_tokens(const uint64_t* src_ptrs, int ep, const StagedTokens& t, const int32_t* num_tokens, int from_row, int to_row,
+                        int tokens_per_rank, int hidden, int num_ctas, uint32_t* status, cudaStream_t stream) {
+    PeerTable src;
+    int rc = fill_table(src, src_ptrs, ep);
+    if (rc != MOK_OK) return rc;
+    if (hidden % 8 != 0 || from_row < 0 || to_row <= from_row || from_row % 256 != 0 || to_row % 256 != 0 || !t.unique_peer ||
+        !t.unique_token || !t.unique_before || !t.staged || t.staged_rows <= 0 || num_tokens == nullptr)
+        return MOK_ERR_INVALID_ARGUMENT;
+    // at most one staged token per row of the range
+    const int grid = comm_grid(to_row - from_row, num_ctas);
+    stage_tokens_kernel<<<grid, 256, 0, stream>>>(src, t.unique_peer, t.unique_token, t.unique_before, num_tokens, from_row, to_row,
+                                                  ep, t.self_rank, tokens_per_rank, hidden, t.staged_rows,
+                                                  static_cast<uint4*>(t.staged), status);
+    MOK_LAUNCH_CHECK("stage_tokens_kernel");
+    return MOK_OK;
+}
+
 int launch_dispatch(const uint64_t* src_ptrs, const uint64_t* weight_ptrs, int ep, const RowWindow& w, int topk,
-                    int tokens_per_rank, int hidden, void* dst, float* row_weight, int num_ctas, cudaStream_t stream) {
+                    int tokens_per_rank, int hidden, void* dst, float* row_weight, int num_ctas, cudaStream_t stream,
+                    const StagedTokens* staged) {
     PeerTable src, wt{};
     int rc = fill_table(src, src_ptrs, ep);
     if (rc != MOK_OK) return rc;
     if (hidden % 8 != 0 || w.row_end <= w.row_begin) return MOK_ERR_INVALID_ARGUMENT;
+    if (staged != nullptr && (!staged->row_source || !staged->staged || staged->staged_rows <= 0)) return MOK_ERR_INVALID_ARGUMENT;
+    const int* row_source = staged ? staged->row_source : nullptr;
+    const uint4* staged_rows_ptr = staged ? static_cast<const uint4*>(staged->staged) : nullptr;
+    const int n_staged = staged ? staged->staged_rows : 0, self = staged ? staged->self_rank : -1;
     const int grid = comm_grid(w.row_end - w.row_begin, num_ctas);
     if (weight_ptrs != nullptr) {
         if ((rc = fill_table(wt, weight_ptrs, ep)) != MOK_OK) return rc;
         dispatch_kernel<true><<<grid, 256, 0, stream>>>(src, wt, w.peer_rank, w.peer_token, w.num_tokens, w.row_begin,
                                                         w.row_end, ep, topk, tokens_per_rank, hidden,
-                                                        static_cast<uint4*>(dst), row_weight, w.status);
+                                                        static_cast<uint4*>(dst), row_weight, w.status, row_source,
+                                                        staged_rows_ptr, n_staged, self);
     } else {
         dispatch_kernel<false><<<grid, 256, 0, stream>>>(src, wt, w.peer_rank, w.peer_token, w.num_tokens, w.row_begin,
                                                          w.row_end, ep, topk, tokens_per_rank, hidden,
-                                                         static_cast<uint4*>(dst), nullptr, w.status);
+                                                         static_cast<uint4*>(dst), nullptr, w.status, row_source,
+                                                         staged_rows_ptr, n_staged, self);
     }
     MOK_LAUNCH_CHECK("dispatch_kernel");
     return MOK_OK;
@@ -252,4 +322,27 @@ extern "C" int mok_combine_rows(const uint64_t* dst_ptrs, const uint64_t* scalar
     const mok::RowWindow w{peer_rank, peer_token_idx, num_tokens, row_begin, row_end, status};
     return mok::launch_combine(dst_ptrs, scalar_ptrs, ep_size, w, topk, num_local_tokens, hidden, src, row_scalar, num_ctas,
                                reinterpret_cast<cudaStream_t>(stream));
+}
+
+extern "C" int mok_stage_unique_rows(const uint64_t* src_ptrs, int ep_size, int rank, const int32_t* unique_peer,
+                                     const int32_t* unique_token, const int32_t* unique_before, const int32_t* num_tokens,
+                                     int from_row, int to_row, int num_local_tokens, int hidden, void* staged, int staged_rows,
+                                     int num_ctas, uint32_t* status, mok_stream_t stream) {
+    mok::StagedTokens t{nullptr, unique_peer, unique_token, unique_before, staged, staged_rows, rank};
+    return mok::launch_stage_tokens(src_ptrs, ep_size, t, num_tokens, from_row, to_row, num_local_tokens, hidden, num_ctas, status,
+                                    reinterpret_cast<cudaStream_t>(stream));
+}
+
+extern "C" int mok_dispatch_rows_staged(const uint64_t* src_ptrs, const uint64_t* weight_ptrs, int ep_size, int rank,
+                                        const int32_t* peer_rank, const int32_t* peer_token_idx, const int32_t* num_tokens,
+                                        const int32_t* row_source, const void* staged, int staged_rows, int row_begin, int row_end,
+                                        int topk, int num_local_tokens, int hidden, void* dst, float* row_weight, int num_ctas,
+                                        uint32_t* status, mok_stream_t stream) {
+    if (peer_rank == nullptr || peer_token_idx == nullptr || num_tokens == nullptr || dst == nullptr || topk <= 0 ||
+        num_local_tokens <= 0 || (weight_ptrs != nullptr && row_weight == nullptr) || rank < 0 || rank >= ep_size)
+        return MOK_ERR_INVALID_ARGUMENT;
+    const mok::RowWindow w{peer_rank, peer_token_idx, num_tokens, row_begin, row_end, status};
+    const mok::StagedTokens t{row_source, nullptr, nullptr, nullptr, const_cast<void*>(staged), staged_rows, rank};
+    return mok::launch_dispatch(src_ptrs, weight_ptrs, ep_size, w, topk, num_local_tokens, hidden, dst, row_weight, num_ctas,
+                                reinterpret_cast<cudaStream_t>(stream), &t);
 }

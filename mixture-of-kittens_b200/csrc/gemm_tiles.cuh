@@ -16,6 +16,7 @@ constexpr int NUM_THREADS = 192;
 constexpr int TMEM_COLS = 512;
 constexpr int MODE_ROWS = 0;   // D[row, :] over schedule rows grouped by expert
 constexpr int MODE_WGRAD = 1;  // D[e] = sum over the rows of expert e
+constexpr int kWgradGroup = 8; // weight-gradient tile order: width of a group of the faster-running tile dimension
 
 struct KernelParams {
     const int32_t* tokens_per_expert;
@@ -52,7 +53,8 @@ struct Tile {
 };
 
 // Tile t of the static list.  rows: m tile major, then output set, then n tile, so that the tiles running at one
-// time share an expert's weights in L2.  wgrad: expert major.  Returns false for tiles without work.
+// time share an expert's weights in L2.  wgrad: expert major, then as described below.  Returns false for tiles
+// without work.
 // (host-callable too: tests/tile_math_host.cu walks the tile lists on the CPU)
 template <int MODE, int BK>
 __host__ __device__ __forceinline__ bool decode_tile(const KernelParams& p, const int* cum, int lo, int hi, int t, Tile& tile) {
@@ -81,10 +83,22 @@ __host__ __device__ __forceinline__ bool decode_tile(const KernelParams& p, cons
         const int per_e = p.m_blocks_w * p.n_blocks;
         const int e = t / per_e;
         const int rem = t - e * per_e;
-        const int mi = rem / p.n_blocks;
+        // Order of an expert's output tiles: the tiles that run at one time (one per CTA pair) should share as few
+        // operand panels as possible, so that the panels (K x 256 each, megabytes when an expert holds thousands of
+        // rows) stay in L2: the dimension with fewer tiles runs fastest, in groups of at most kWgradGroup, the other
+        // dimension next, the groups slowest.  74 pairs then touch about 8 + 9 panels instead of up to 28 + 3.
+        const bool m_inner = p.m_blocks_w <= p.n_blocks;
+        const int d_in = m_inner ? p.m_blocks_w : p.n_blocks;
+        const int d_out = m_inner ? p.n_blocks : p.m_blocks_w;
+        const int group = d_in <= kWgradGroup + kWgradGroup / 2 ? d_in : kWgradGroup;
+        const int g = rem / (group * d_out);
+        const int width = min(group, d_in - g * group);
+        const int r2 = rem - g * group * d_out;
+        const int outer = r2 / width;
+        const int inner = g * group + (r2 - outer * width);
         tile.expert = e;
-        tile.m0 = mi * BM;
-        tile.n0 = (rem - mi * p.n_blocks) * BN;
+        tile.m0 = (m_inner ? inner : outer) * BM;
+        tile.n0 = (m_inner ? outer : inner) * BN;
         tile.set = 0;
         const int ks = max(cum[e], lo);
         int ke = min(cum[e + 1], hi);

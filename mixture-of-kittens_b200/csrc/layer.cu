@@ -274,10 +274,50 @@ int comm_ctas(const mok_layer_args* a, bool overlapped) {
     return a->num_comm_sms * 8;
 }
 
+// ---- de-duplicated dispatch ------------------------------------------------------------------------------
+// With the index arrays of mok_schedule_dedup in the arguments and more than one rank, a dispatch first stages the
+// tokens its rows use (each pulled over NVLink once) and then fans them out with local copies.  Staged tokens are
+// numbered by first row, so "everything rows below r need" is a prefix of the staging buffer: `Staging` remembers how
+// far that prefix has been filled during the current call (per source buffer: x or d_y).
+struct Staging {
+    int staged_upto_row = 0;
+};
+
+bool dedup_enabled(const mok_layer_args* a) {
+    return a->ep_size > 1 && a->row_source && a->unique_peer && a->unique_token && a->unique_before && a->staged_rows > 0;
+}
+
+StagedTokens staged_tokens(const mok_layer_args* a, void* buffer) {
+    return StagedTokens{a->row_source, a->unique_peer, a->unique_token, a->unique_before, buffer, a->staged_rows, a->rank};
+}
+
+// Makes sure the tokens used by rows below s.end are in `buffer`, then copies the rows of the span.
+int staged_dispatch(const mok_layer_args* a, const uint64_t* src_ptrs, const uint64_t* weight_ptrs, void* buffer, Staging* state,
+                    const Span& s, void* dst, float* row_weight, int ctas, cudaStream_t st) {
+    const StagedTokens t = staged_tokens(a, buffer);
+    if (s.end > state->staged_upto_row) {
+        MOK_TRY(launch_stage_tokens(src_ptrs, a->ep_size, t, a->num_tokens, state->staged_upto_row, s.end, a->num_local_tokens,
+                                    a->hidden, ctas, a->status, st));
+        state->staged_upto_row = s.end;
+    }
+    return launch_dispatch(src_ptrs, weight_ptrs, a->ep_size, rows_of(a, s), a->topk, a->num_local_tokens, a->hidden, dst,
+                           row_weight, ctas, st, &t);
+}
+
 // ---- per-span building blocks ---------------------------------------------------------------------------
-int dispatch_x(const mok_layer_args* a, const Span& s, int ctas, cudaStream_t st) {
+int dispatch_x(const mok_layer_args* a, const Span& s, int ctas, cudaStream_t st, Staging* staging) {
+    if (dedup_enabled(a) && a->staged_x != nullptr)
+        return staged_dispatch(a, a->x_ptrs, nullptr, a->staged_x, staging, s, rows_bf16(a->x_routed, s, a->hidden), nullptr, ctas, st);
     return launch_dispatch(a->x_ptrs, nullptr, a->ep_size, rows_of(a, s), a->topk, a->num_local_tokens, a->hidden,
                            rows_bf16(a->x_routed, s, a->hidden), nullptr, ctas, st);
+}
+
+int dispatch_d_y(const mok_layer_args* a, const Span& s, float* row_weight, int ctas, cudaStream_t st, Staging* staging) {
+    void* dst = rows_bf16(a->d_y_routed, s, a->hidden);
+    if (dedup_enabled(a) && a->staged_d_y != nullptr)
+        return staged_dispatch(a, a->d_y_ptrs, a->router_weight_ptrs, a->staged_d_y, staging, s, dst, at_row(row_weight, s, 1), ctas, st);
+    return launch_dispatch(a->d_y_ptrs, a->router_weight_ptrs, a->ep_size, rows_of(a, s), a->topk, a->num_local_tokens, a->hidden,
+                           dst, at_row(row_weight, s, 1), ctas, st);
 }
 
 int gate_up_hidden(const mok_layer_args* a, const Span& s, cudaStream_t st) {
@@ -496,6 +536,7 @@ extern "C" int mok_moe_forward_bf16(const mok_layer_args* a, mok_stream_t stream
     if (!a->combine_ptrs || !a->w_routed_down || !a->y_routed) return MOK_ERR_INVALID_ARGUMENT;
     if (a->w_shared_gate && (!a->w_shared_down || !a->y_shared)) return MOK_ERR_INVALID_ARGUMENT;
     cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+    Staging x_staging, d_y_staging;   // how far the de-duplicated tokens of x / d_y have been staged in this call
     const bool overlapped = overlap_enabled();
     DeviceStreams* d = nullptr;
     CommFork fork;   // the internal stream starts after the caller's earlier work and is joined on every way out
@@ -510,7 +551,7 @@ extern "C" int mok_moe_forward_bf16(const mok_layer_args* a, mok_stream_t stream
         const Span win = window_span(a, wi);
         MOK_TRY(run_chunks(
             a, win, overlapped, d, s,
-            [&](const Span& c, int ctas, cudaStream_t st) { return dispatch_x(a, c, ctas, st); },
+            [&](const Span& c, int ctas, cudaStream_t st) { return dispatch_x(a, c, ctas, st, &x_staging); },
             [&](const Span& c, cudaStream_t st) {
                 MOK_TRY(gate_up_hidden(a, c, st));
                 return launch_rows_gemm(routed_problem(a, c), rows_bf16(a->hidden_routed, c, I), I, a->w_routed_down, nullptr,
@@ -533,9 +574,10 @@ extern "C" int mok_moe_recompute_bf16(const mok_layer_args* a, mok_stream_t stre
     using namespace mok;
     MOK_TRY(check_common(a));
     cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+    Staging x_staging, d_y_staging;   // how far the de-duplicated tokens of x / d_y have been staged in this call
     if (a->w_shared_gate) MOK_TRY(shared_up_to_hidden(a, s));
     const Span win = window_span(a, 0);
-    MOK_TRY(dispatch_x(a, win, 0, s));
+    MOK_TRY(dispatch_x(a, win, 0, s, &x_staging));
     MOK_TRY(gate_up_hidden(a, win, s));
     return MOK_OK;
 }
@@ -553,6 +595,7 @@ extern "C" int mok_moe_backward_bf16(const mok_layer_args* a, mok_stream_t strea
                     a->d_w_shared_gate && a->d_w_shared_up && a->d_w_shared_down))
         return MOK_ERR_INVALID_ARGUMENT;
     cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+    Staging x_staging, d_y_staging;   // how far the de-duplicated tokens of x / d_y have been staged in this call
     const int H = a->hidden, I = a->intermediate, T = a->num_local_tokens;
     const bool clamp = a->has_swiglu_limit != 0;
     const bool overlapped = overlap_enabled();
@@ -574,15 +617,12 @@ extern "C" int mok_moe_backward_bf16(const mok_layer_args* a, mok_stream_t strea
     for (int wi = 0; wi < num_windows(a); ++wi) {
         const Span win = window_span(a, wi);
         if (wi > 0) {   // the saved context only covers window 0: rebuild x_routed, gate, up, hidden of this window
-            MOK_TRY(dispatch_x(a, win, 0, s));
+            MOK_TRY(dispatch_x(a, win, 0, s, &x_staging));
             MOK_TRY(gate_up_hidden(a, win, s));
         }
         MOK_TRY(run_chunks(
             a, win, overlapped, d, s,
-            [&](const Span& c, int ctas, cudaStream_t st) {
-                return launch_dispatch(a->d_y_ptrs, a->router_weight_ptrs, a->ep_size, rows_of(a, c), a->topk, T, H,
-                                       rows_bf16(a->d_y_routed, c, H), at_row(row_weight, c, 1), ctas, st);
-            },
+            [&](const Span& c, int ctas, cudaStream_t st) { return dispatch_d_y(a, c, row_weight, ctas, st, &d_y_staging); },
             [&](const Span& c, cudaStream_t st) {
                 const GemmProblem p = routed_problem(a, c);
                 MOK_TRY(launch_rows_gemm(p, rows_bf16(a->d_y_routed, c, H), H, a->w_routed_down, nullptr,
@@ -626,6 +666,7 @@ extern "C" int mok_moe_forward_mxfp8(const mok_layer_args* a, mok_stream_t strea
     if (!a->combine_ptrs || !a->w_down_fp8 || !a->w_down_sc || !a->y_routed) return MOK_ERR_INVALID_ARGUMENT;
     if (a->w_shared_gate && (!a->w_shared_down || !a->y_shared)) return MOK_ERR_INVALID_ARGUMENT;
     cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+    Staging x_staging, d_y_staging;   // how far the de-duplicated tokens of x / d_y have been staged in this call
     const bool overlapped = overlap_enabled();
     DeviceStreams* d = nullptr;
     CommFork fork;
@@ -641,7 +682,7 @@ extern "C" int mok_moe_forward_mxfp8(const mok_layer_args* a, mok_stream_t strea
         const Span win = window_span(a, wi);
         MOK_TRY(run_chunks(
             a, win, overlapped, d, s,
-            [&](const Span& c, int ctas, cudaStream_t st) { return dispatch_x(a, c, ctas, st); },
+            [&](const Span& c, int ctas, cudaStream_t st) { return dispatch_x(a, c, ctas, st, &x_staging); },
             [&](const Span& c, cudaStream_t st) {
                 MOK_TRY(gate_up_hidden_mxfp8(a, c, st));
                 return launch_fp8_rows_gemm(routed_problem(a, c), act_rows(a, a->hidden_fp8, a->hidden_sc, I, c), I, wd, nullptr,
@@ -664,9 +705,10 @@ extern "C" int mok_moe_recompute_mxfp8(const mok_layer_args* a, mok_stream_t str
     MOK_TRY(check_common(a, true));
     MOK_TRY(check_mxfp8_forward_fields(a));
     cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+    Staging x_staging, d_y_staging;   // how far the de-duplicated tokens of x / d_y have been staged in this call
     if (a->w_shared_gate) MOK_TRY(shared_up_to_hidden(a, s));
     const Span win = window_span(a, 0);
-    MOK_TRY(dispatch_x(a, win, 0, s));
+    MOK_TRY(dispatch_x(a, win, 0, s, &x_staging));
     MOK_TRY(gate_up_hidden_mxfp8(a, win, s));
     return MOK_OK;
 }
@@ -689,6 +731,7 @@ extern "C" int mok_moe_backward_mxfp8(const mok_layer_args* a, mok_stream_t stre
                     a->d_w_shared_gate && a->d_w_shared_up && a->d_w_shared_down))
         return MOK_ERR_INVALID_ARGUMENT;
     cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+    Staging x_staging, d_y_staging;   // how far the de-duplicated tokens of x / d_y have been staged in this call
     const int H = a->hidden, I = a->intermediate, T = a->num_local_tokens;
     const bool clamp = a->has_swiglu_limit != 0;
     const bool overlapped = overlap_enabled();
@@ -713,15 +756,12 @@ extern "C" int mok_moe_backward_mxfp8(const mok_layer_args* a, mok_stream_t stre
     for (int wi = 0; wi < num_windows(a); ++wi) {
         const Span win = window_span(a, wi);
         if (wi > 0) {
-            MOK_TRY(dispatch_x(a, win, 0, s));
+            MOK_TRY(dispatch_x(a, win, 0, s, &x_staging));
             MOK_TRY(gate_up_hidden_mxfp8(a, win, s));
         }
         MOK_TRY(run_chunks(
             a, win, overlapped, d, s,
-            [&](const Span& c, int ctas, cudaStream_t st) {
-                return launch_dispatch(a->d_y_ptrs, a->router_weight_ptrs, a->ep_size, rows_of(a, c), a->topk, T, H,
-                                       rows_bf16(a->d_y_routed, c, H), at_row(row_weight, c, 1), ctas, st);
-            },
+            [&](const Span& c, int ctas, cudaStream_t st) { return dispatch_d_y(a, c, row_weight, ctas, st, &d_y_staging); },
             [&](const Span& c, cudaStream_t st) {
                 const GemmProblem p = routed_problem(a, c);
                 const long long off = c.begin - c.base;

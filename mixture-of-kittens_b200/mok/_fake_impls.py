@@ -30,6 +30,15 @@ def _(topk_all, num_local_experts, schedule_capacity, rank):
             topk_all.new_empty((1,), **i32), topk_all.new_empty((num_local_experts,), **i32))
 
 
+@torch.library.register_fake("mok::schedule_dedup")
+def _(topk_all, schedule_peer_rank, schedule_peer_token_idx, num_tokens, num_local_experts, rank):
+    i32 = dict(dtype=torch.int32)
+    cap = schedule_peer_rank.shape[0]
+    unique = min(cap, topk_all.shape[0] * topk_all.shape[1])
+    return (topk_all.new_empty((cap,), **i32), topk_all.new_empty((unique,), **i32), topk_all.new_empty((unique,), **i32),
+            topk_all.new_empty((cap // 256 + 1,), **i32), topk_all.new_empty((1,), **i32))
+
+
 @torch.library.register_fake("mok::mxfp8_quantize")
 def _(x_bf16, return_normal, return_transposed):
     e = x_bf16.shape[0] if x_bf16.ndim == 3 else 1
@@ -63,27 +72,31 @@ def _fwd_bf16_context(x, w_shared_gate, macrobatch_size):
 def _(x, x_ptrs, combine_buffer, combine_buffer_ptrs, w_shared_gate, w_routed_gate, w_routed_gate_sc, w_shared_up,
       w_routed_up, w_routed_up_sc, w_shared_down, w_routed_down, w_routed_down_sc, schedule_peer_rank,
       schedule_peer_token_idx, num_tokens, tokens_per_expert, topk, swiglu_limit, num_comm_sms, macrobatch_size,
-      minibatch_size):
+      minibatch_size, dedup_row_source=None, dedup_unique_peer=None,
+      dedup_unique_token=None, dedup_unique_before=None):
     return _fwd_mxfp8_context(x, w_shared_gate, macrobatch_size) + (x.new_empty(x.shape), x.new_empty((macrobatch_size, x.shape[1])))
 
 
 @torch.library.register_fake("mok::dispatch_mlp_swiglu_combine_fwd_bf16")
 def _(x, x_ptrs, combine_buffer, combine_buffer_ptrs, w_shared_gate, w_routed_gate, w_shared_up, w_routed_up,
       w_shared_down, w_routed_down, schedule_peer_rank, schedule_peer_token_idx, num_tokens, tokens_per_expert, topk,
-      swiglu_limit, num_comm_sms, macrobatch_size, minibatch_size):
+      swiglu_limit, num_comm_sms, macrobatch_size, minibatch_size, dedup_row_source=None, dedup_unique_peer=None,
+      dedup_unique_token=None, dedup_unique_before=None):
     return _fwd_bf16_context(x, w_shared_gate, macrobatch_size) + (x.new_empty(x.shape), x.new_empty((macrobatch_size, x.shape[1])))
 
 
 @torch.library.register_fake("mok::recompute_forward_context_mxfp8")
 def _(x, x_ptrs, w_shared_gate, w_routed_gate, w_routed_gate_sc, w_shared_up, w_routed_up, w_routed_up_sc,
       schedule_peer_rank, schedule_peer_token_idx, num_tokens, tokens_per_expert, topk, swiglu_limit, num_comm_sms,
-      macrobatch_size, minibatch_size):
+      macrobatch_size, minibatch_size, dedup_row_source=None, dedup_unique_peer=None,
+      dedup_unique_token=None, dedup_unique_before=None):
     return _fwd_mxfp8_context(x, w_shared_gate, macrobatch_size)
 
 
 @torch.library.register_fake("mok::recompute_forward_context_bf16")
 def _(x, x_ptrs, w_shared_gate, w_routed_gate, w_shared_up, w_routed_up, schedule_peer_rank, schedule_peer_token_idx,
-      num_tokens, tokens_per_expert, topk, swiglu_limit, num_comm_sms, macrobatch_size, minibatch_size):
+      num_tokens, tokens_per_expert, topk, swiglu_limit, num_comm_sms, macrobatch_size, minibatch_size, dedup_row_source=None, dedup_unique_peer=None,
+      dedup_unique_token=None, dedup_unique_before=None):
     return _fwd_bf16_context(x, w_shared_gate, macrobatch_size)
 
 
@@ -99,7 +112,8 @@ def _(d_y_buffer, d_y_buffer_ptrs, d_x_routed_buffer, d_x_routed_buffer_ptrs, ro
       w_routed_down_T_sc, x_fp8_t_routed, x_sc_t_routed, gate_shared, gate_fp8_routed, gate_sc_routed, up_shared,
       up_fp8_routed, up_sc_routed, hidden_shared, hidden_fp8_t_routed, hidden_sc_t_routed, x, x_ptrs, w_routed_gate,
       w_routed_gate_sc, w_routed_up, w_routed_up_sc, schedule_peer_rank, schedule_peer_token_idx, num_tokens,
-      tokens_per_expert, topk, swiglu_limit, num_comm_sms, macrobatch_size, minibatch_size):
+      tokens_per_expert, topk, swiglu_limit, num_comm_sms, macrobatch_size, minibatch_size, dedup_row_source=None, dedup_unique_peer=None,
+      dedup_unique_token=None, dedup_unique_before=None):
     d = d_y_buffer
     t, h = d.shape
     i = w_shared_gate.shape[0]
@@ -116,7 +130,8 @@ def _(d_y_buffer, d_y_buffer_ptrs, d_x_routed_buffer, d_x_routed_buffer_ptrs, ro
       router_weight_buffer_ptrs, d_router_weight_buffer, d_router_weight_buffer_ptrs, w_shared_gate, w_routed_gate,
       w_shared_up, w_routed_up, w_shared_down, w_routed_down, x_routed, gate_shared, gate_routed, up_shared, up_routed,
       hidden_shared, hidden_routed, x, x_ptrs, schedule_peer_rank, schedule_peer_token_idx, num_tokens,
-      tokens_per_expert, topk, swiglu_limit, num_comm_sms, macrobatch_size, minibatch_size):
+      tokens_per_expert, topk, swiglu_limit, num_comm_sms, macrobatch_size, minibatch_size, dedup_row_source=None, dedup_unique_peer=None,
+      dedup_unique_token=None, dedup_unique_before=None):
     d = d_y_buffer
     t, h = d.shape
     i = w_shared_gate.shape[0]

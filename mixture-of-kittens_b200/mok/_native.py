@@ -45,7 +45,9 @@ class LayerArgs(ctypes.Structure):
             "w_gate_t_fp8", "w_gate_t_sc", "w_up_t_fp8", "w_up_t_sc", "w_down_t_fp8", "w_down_t_sc",
             "x_fp8", "x_sc", "x_fp8_t", "x_sc_t", "gate_fp8", "gate_sc", "up_fp8", "up_sc",
             "hidden_fp8", "hidden_sc", "hidden_fp8_t", "hidden_sc_t", "d_y_fp8", "d_y_sc", "d_y_fp8_t", "d_y_sc_t",
-            "d_gate_fp8", "d_gate_sc", "d_up_fp8", "d_up_sc", "d_gate_fp8_t", "d_gate_sc_t", "d_up_fp8_t", "d_up_sc_t")]
+            "d_gate_fp8", "d_gate_sc", "d_up_fp8", "d_up_sc", "d_gate_fp8_t", "d_gate_sc_t", "d_up_fp8_t", "d_up_sc_t",
+            "row_source", "unique_peer", "unique_token", "unique_before", "staged_x", "staged_d_y")]
+        + [("staged_rows", c_int), ("reserved1", c_int)]
     )
 
 
@@ -66,6 +68,17 @@ def lib() -> ctypes.CDLL:
         L.mok_schedule_static.argtypes = [c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p,
                                           c_void_p, c_void_p, c_void_p]
         L.mok_schedule_static.restype = c_int
+        L.mok_schedule_dedup_scratch_bytes.restype = c_int64
+        L.mok_schedule_dedup_scratch_bytes.argtypes = [c_int, c_int, c_int, c_int]
+        L.mok_schedule_dedup.argtypes = [c_void_p] + [c_int] * 6 + [c_void_p] * 8 + [c_int, c_void_p, c_void_p]
+        L.mok_schedule_dedup.restype = c_int
+        L.mok_stage_unique_rows.argtypes = [POINTER(c_uint64), c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
+                                            c_int, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p]
+        L.mok_stage_unique_rows.restype = c_int
+        L.mok_dispatch_rows_staged.argtypes = [POINTER(c_uint64), POINTER(c_uint64), c_int, c_int, c_void_p, c_void_p, c_void_p,
+                                               c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p,
+                                               c_int, c_void_p, c_void_p]
+        L.mok_dispatch_rows_staged.restype = c_int
         L.mok_all_gather_top_experts.argtypes = [c_void_p, c_int64, POINTER(c_uint64), c_int, c_int, c_void_p]
         L.mok_barrier_all.argtypes = [c_void_p, POINTER(c_uint64), c_int, c_void_p, c_void_p, c_int, c_void_p]
         L.mok_fwd_epilogue.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_void_p, c_void_p]

@@ -10,6 +10,7 @@ address); kernels report problems through `mok.ops.check_status()` instead of tr
 from __future__ import annotations
 
 import math
+import os
 from dataclasses import dataclass, field
 from typing import Any
 
@@ -29,6 +30,7 @@ from .ops import (
     recompute_forward_context_bf16,
     recompute_forward_context_mxfp8,
     schedule,
+    schedule_dedup,
 )
 
 SUPPORTED_EP_SIZES = _ops.SUPPORTED_EP_SIZES
@@ -50,6 +52,13 @@ class MoKSchedule:                     # reference :34-39
     peer_token_idx: torch.Tensor     # (schedule_capacity,) int32, token * topk + k on the source rank
     num_tokens: torch.Tensor         # (1,) int32, padded total (stays on the device)
     tokens_per_expert: torch.Tensor  # (num_local_experts,) int32, each padded to 256
+    # De-duplicated dispatch (not in the reference, whose dispatch pulls a token once per route): built for EP > 1
+    # unless MOK_NO_DEDUP=1.  Every (source rank, token) this rank serves is numbered in the order of its first row.
+    row_source: torch.Tensor | None = None      # (schedule_capacity,) int32 number of the row's token, -1 on padding rows
+    unique_peer: torch.Tensor | None = None     # (U,) int32 source rank of staged token u
+    unique_token: torch.Tensor | None = None    # (U,) int32 its token index on that rank
+    unique_before: torch.Tensor | None = None   # (schedule_capacity / 256 + 1,) int32 tokens first used below row 256 * i
+    num_unique: torch.Tensor | None = None      # (1,) int32
 
 
 @dataclass(frozen=True, slots=True)
@@ -300,8 +309,14 @@ def build_schedule(workspace: MoKWorkspace, config: MoKConfig, top_experts: torc
     _barrier(workspace)
     peer_rank, peer_token_idx, num_tokens, tokens_per_expert = schedule(
         workspace.all_gather_top_experts_buffer, num_local_experts, workspace.schedule_capacity, workspace.ep_rank)
+    if workspace.ep_size == 1 or os.environ.get("MOK_NO_DEDUP") == "1":
+        return MoKSchedule(peer_rank=peer_rank, peer_token_idx=peer_token_idx, num_tokens=num_tokens,
+                           tokens_per_expert=tokens_per_expert)
+    row_source, unique_peer, unique_token, unique_before, num_unique = schedule_dedup(
+        workspace.all_gather_top_experts_buffer, peer_rank, peer_token_idx, num_tokens, num_local_experts, workspace.ep_rank)
     return MoKSchedule(peer_rank=peer_rank, peer_token_idx=peer_token_idx, num_tokens=num_tokens,
-                       tokens_per_expert=tokens_per_expert)
+                       tokens_per_expert=tokens_per_expert, row_source=row_source, unique_peer=unique_peer,
+                       unique_token=unique_token, unique_before=unique_before, num_unique=num_unique)
 
 
 def validate_inputs(config: MoKConfig, workspace: MoKWorkspace, schedule: MoKSchedule, x: torch.Tensor,
@@ -341,7 +356,8 @@ def forward(config: MoKConfig, workspace: MoKWorkspace, schedule: MoKSchedule, x
     _barrier(workspace)   # every peer's x is in place before anyone pulls
 
     sched = (schedule.peer_rank, schedule.peer_token_idx, schedule.num_tokens, schedule.tokens_per_expert)
-    tail = (workspace.topk, swiglu_limit, config.fwd_num_comm_sms, config.macrobatch_size, config.minibatch_size)
+    tail = (workspace.topk, swiglu_limit, config.fwd_num_comm_sms, config.macrobatch_size, config.minibatch_size,
+            schedule.row_source, schedule.unique_peer, schedule.unique_token, schedule.unique_before)
     if isinstance(routed_gate_weights, tuple):
         g_fp8, g_sc = routed_gate_weights
         u_fp8, u_sc = routed_up_weights
@@ -382,7 +398,8 @@ def recompute_forward_context(config: MoKConfig, workspace: MoKWorkspace, schedu
     _barrier(workspace)
 
     sched = (schedule.peer_rank, schedule.peer_token_idx, schedule.num_tokens, schedule.tokens_per_expert)
-    tail = (workspace.topk, swiglu_limit, config.fwd_num_comm_sms, config.macrobatch_size, config.minibatch_size)
+    tail = (workspace.topk, swiglu_limit, config.fwd_num_comm_sms, config.macrobatch_size, config.minibatch_size,
+            schedule.row_source, schedule.unique_peer, schedule.unique_token, schedule.unique_before)
     if isinstance(routed_gate_weights, tuple):
         g_fp8, g_sc = routed_gate_weights
         u_fp8, u_sc = routed_up_weights
@@ -427,7 +444,8 @@ def backward(config: MoKConfig, workspace: MoKWorkspace, schedule: MoKSchedule, 
             workspace.router_weight_buffer, workspace.router_weight_buffer_ptrs,
             workspace.d_router_weight_buffer, workspace.d_router_weight_buffer_ptrs)
     sched = (schedule.peer_rank, schedule.peer_token_idx, schedule.num_tokens, schedule.tokens_per_expert)
-    tail = (workspace.topk, swiglu_limit, config.bwd_num_comm_sms, config.macrobatch_size, config.minibatch_size)
+    tail = (workspace.topk, swiglu_limit, config.bwd_num_comm_sms, config.macrobatch_size, config.minibatch_size,
+            schedule.row_source, schedule.unique_peer, schedule.unique_token, schedule.unique_before)
     ctx = forward_context
     if isinstance(routed_gate_weights, tuple):
         g_fp8, g_sc, g_t_fp8, g_t_sc = routed_gate_weights

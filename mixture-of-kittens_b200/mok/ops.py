@@ -297,6 +297,80 @@ def schedule(
     return peer_rank, peer_token, num_tokens, per_expert
 
 
+def _attach_dedup(args: LayerArgs, x: torch.Tensor, capacity: int, which: tuple[str, ...], need_x: bool, row_source, unique_peer,
+                  unique_token, unique_before):
+    """Sets the de-duplicated-dispatch fields of the layer arguments (all four index tensors or none) and allocates the
+    staging buffers the call needs: one [staged_rows, H] bf16 buffer per staged input (`which`: "x", "d_y"; the x buffer
+    of a backward call only when later macrobatches are replayed)."""
+    given = [t is not None for t in (row_source, unique_peer, unique_token, unique_before)]
+    if not any(given) or args.ep_size == 1:
+        return None
+    _require(all(given), "the four dedup_* tensors must be given together")
+    for name, t in (("dedup_row_source", row_source), ("dedup_unique_peer", unique_peer), ("dedup_unique_token", unique_token),
+                    ("dedup_unique_before", unique_before)):
+        _require(t.device == x.device and t.dtype == torch.int32 and t.is_contiguous() and t.ndim == 1,
+                 f"{name} must be a contiguous 1D int32 tensor on {x.device}")
+    _require(row_source.numel() == capacity, "dedup_row_source must have schedule_capacity entries")
+    _require(unique_before.numel() == capacity // 256 + 1, "dedup_unique_before must have schedule_capacity / 256 + 1 entries")
+    _require(unique_peer.numel() == unique_token.numel() and unique_peer.numel() > 0,
+             "dedup_unique_peer and dedup_unique_token must have the same, positive length")
+    staged_rows = unique_peer.numel()
+    _set_ptrs(args, row_source=row_source, unique_peer=unique_peer, unique_token=unique_token, unique_before=unique_before)
+    args.staged_rows = staged_rows
+    buffers = []
+    if "x" in which and need_x:
+        buffers.append(x.new_empty((staged_rows, x.shape[1])))
+        args.staged_x = buffers[-1].data_ptr()
+    if "d_y" in which:
+        buffers.append(x.new_empty((staged_rows, x.shape[1])))
+        args.staged_d_y = buffers[-1].data_ptr()
+    return buffers
+
+
+@torch.library.custom_op("mok::schedule_dedup", mutates_args=())
+def schedule_dedup(
+    topk_all: torch.Tensor,
+    schedule_peer_rank: torch.Tensor,
+    schedule_peer_token_idx: torch.Tensor,
+    num_tokens: torch.Tensor,
+    num_local_experts: int,
+    rank: int,
+) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor]:
+    """Extends a schedule for de-duplicated dispatch: every (source rank, token) this rank serves is numbered in the
+    order of its first schedule row, so that dispatch can pull each token once and fan it out locally.  Not among the
+    reference ops (its dispatch pulls one row per route).
+
+    Inputs:  topk_all int32 [ep_size, num_local_tokens, topk] and the outputs of `schedule`
+    Outputs: row_source [cap] (number of the row's token, -1 on padding rows), unique_peer [U], unique_token [U]
+             (source rank and token index of staged token u; U = min(cap, ep_size * num_local_tokens)),
+             unique_before [cap / 256 + 1] (staged tokens first used below row 256 * i), num_unique [1]  (all int32)
+    """
+    _require(topk_all.ndim == 3 and topk_all.is_cuda and topk_all.dtype == torch.int32 and topk_all.is_contiguous(),
+             "topk_all must be a contiguous CUDA int32 tensor of shape (ep_size, num_local_tokens, topk)")
+    ep_size, num_local_tokens, topk = topk_all.shape
+    _require(ep_size in SUPPORTED_EP_SIZES, f"topk_all ep_size must be one of {SUPPORTED_EP_SIZES}")
+    cap = _check_schedule(schedule_peer_rank)
+    for name, t, shape in (("schedule_peer_rank", schedule_peer_rank, (cap,)), ("schedule_peer_token_idx", schedule_peer_token_idx, (cap,)),
+                           ("num_tokens", num_tokens, (1,))):
+        _require(t.device == topk_all.device and t.dtype == torch.int32 and t.is_contiguous() and tuple(t.shape) == shape,
+                 f"{name} must be contiguous int32 {shape} on {topk_all.device}")
+    _require(type(num_local_experts) is int and num_local_experts > 0, "num_local_experts must be a positive integer")
+    _require(type(rank) is int and 0 <= rank < ep_size, "rank must be an integer in [0, ep_size)")
+    opts = dict(dtype=torch.int32, device=topk_all.device)
+    max_unique = min(cap, ep_size * num_local_tokens)
+    row_source = torch.empty(cap, **opts)
+    unique_peer = torch.empty(max_unique, **opts)
+    unique_token = torch.empty(max_unique, **opts)
+    unique_before = torch.empty(cap // 256 + 1, **opts)
+    num_unique = torch.empty(1, **opts)
+    scratch = torch.empty(lib().mok_schedule_dedup_scratch_bytes(ep_size, num_local_tokens, topk, cap) // 4, **opts)
+    check(lib().mok_schedule_dedup(ptr(topk_all), ep_size, num_local_tokens, topk, num_local_experts, cap, rank,
+                                   ptr(schedule_peer_rank), ptr(schedule_peer_token_idx), ptr(num_tokens), ptr(row_source),
+                                   ptr(unique_peer), ptr(unique_token), ptr(unique_before), ptr(num_unique), max_unique,
+                                   ptr(scratch), stream_ptr(topk_all.device)), "schedule_dedup")
+    return row_source, unique_peer, unique_token, unique_before, num_unique
+
+
 @torch.library.custom_op(
     "mok::mxfp8_quantize", mutates_args=(),
     schema="(Tensor x_bf16, bool return_normal, bool return_transposed) -> (Tensor?, Tensor?, Tensor?, Tensor?)",
@@ -348,6 +422,10 @@ def dispatch_mlp_swiglu_combine_fwd_bf16(
     num_comm_sms: int,
     macrobatch_size: int,
     minibatch_size: int,
+    dedup_row_source: torch.Tensor | None = None,
+    dedup_unique_peer: torch.Tensor | None = None,
+    dedup_unique_token: torch.Tensor | None = None,
+    dedup_unique_before: torch.Tensor | None = None,
 ) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor,
            torch.Tensor]:
     """BF16 forward: dispatch, routed + shared SwiGLU FFN, combine into the owners' slot buffers.
@@ -390,6 +468,8 @@ def dispatch_mlp_swiglu_combine_fwd_bf16(
     a.x_routed, a.y_routed, a.y_shared = x_routed.data_ptr(), y_routed.data_ptr(), y_shared.data_ptr()
     a.gate_shared, a.up_shared, a.hidden_shared = gate_shared.data_ptr(), up_shared.data_ptr(), hidden_shared.data_ptr()
     a.gate_routed, a.up_routed, a.hidden_routed = gate_routed.data_ptr(), up_routed.data_ptr(), hidden_routed.data_ptr()
+    _staging = _attach_dedup(a, x, cap, ('x',), True, dedup_row_source, dedup_unique_peer, dedup_unique_token,
+                             dedup_unique_before)  # noqa: F841  (keeps the staging buffers alive until the launch is queued)
     check(lib().mok_moe_forward_bf16(_native.ctypes.byref(a), stream_ptr(x.device)), "dispatch_mlp_swiglu_combine_fwd_bf16")
     return (x_routed, gate_shared, gate_routed, up_shared, up_routed, hidden_shared, hidden_routed, y_shared, y_routed)
 
@@ -411,6 +491,10 @@ def recompute_forward_context_bf16(
     num_comm_sms: int,
     macrobatch_size: int,
     minibatch_size: int,
+    dedup_row_source: torch.Tensor | None = None,
+    dedup_unique_peer: torch.Tensor | None = None,
+    dedup_unique_token: torch.Tensor | None = None,
+    dedup_unique_before: torch.Tensor | None = None,
 ) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor]:
     """Rebuilds the saved forward context (first macrobatch) without the down projection and combine.
 
@@ -445,6 +529,8 @@ def recompute_forward_context_bf16(
     a.x_routed = x_routed.data_ptr()
     a.gate_shared, a.up_shared, a.hidden_shared = gate_shared.data_ptr(), up_shared.data_ptr(), hidden_shared.data_ptr()
     a.gate_routed, a.up_routed, a.hidden_routed = gate_routed.data_ptr(), up_routed.data_ptr(), hidden_routed.data_ptr()
+    _staging = _attach_dedup(a, x, cap, ('x',), True, dedup_row_source, dedup_unique_peer, dedup_unique_token,
+                             dedup_unique_before)  # noqa: F841  (keeps the staging buffers alive until the launch is queued)
     check(lib().mok_moe_recompute_bf16(_native.ctypes.byref(a), stream_ptr(x.device)), "recompute_forward_context_bf16")
     return (x_routed, gate_shared, gate_routed, up_shared, up_routed, hidden_shared, hidden_routed)
 
@@ -486,6 +572,10 @@ def dispatch_mlp_swiglu_combine_bwd_bf16(
     num_comm_sms: int,
     macrobatch_size: int,
     minibatch_size: int,
+    dedup_row_source: torch.Tensor | None = None,
+    dedup_unique_peer: torch.Tensor | None = None,
+    dedup_unique_token: torch.Tensor | None = None,
+    dedup_unique_before: torch.Tensor | None = None,
 ) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor,
            torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor]:
     """BF16 backward of the layer.
@@ -551,6 +641,8 @@ def dispatch_mlp_swiglu_combine_bwd_bf16(
     a.d_w_routed_gate, a.d_w_routed_up, a.d_w_routed_down = d_w_routed_gate.data_ptr(), d_w_routed_up.data_ptr(), d_w_routed_down.data_ptr()
     a.row_scratch = row_scratch.data_ptr()
     a.d_y_local = d_y_buffer.data_ptr()
+    _staging = _attach_dedup(a, x, cap, ('x', 'd_y'), macrobatch_size < cap, dedup_row_source, dedup_unique_peer, dedup_unique_token,
+                             dedup_unique_before)  # noqa: F841  (keeps the staging buffers alive until the launch is queued)
     check(lib().mok_moe_backward_bf16(_native.ctypes.byref(a), stream_ptr(x.device)), "dispatch_mlp_swiglu_combine_bwd_bf16")
     return (d_x_shared, d_x_routed, d_gate_shared, d_gate_routed, d_up_shared, d_up_routed, d_hidden_shared, d_hidden_routed,
             d_y_routed, d_w_shared_gate, d_w_routed_gate, d_w_shared_up, d_w_routed_up, d_w_shared_down, d_w_routed_down)
@@ -630,6 +722,10 @@ def dispatch_mlp_swiglu_combine_fwd_mxfp8(
     num_comm_sms: int,
     macrobatch_size: int,
     minibatch_size: int,
+    dedup_row_source: torch.Tensor | None = None,
+    dedup_unique_peer: torch.Tensor | None = None,
+    dedup_unique_token: torch.Tensor | None = None,
+    dedup_unique_before: torch.Tensor | None = None,
 ) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor,
            torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor]:
     """MXFP8 forward (routed experts in e4m3 with e8m0 block scales, shared expert in bf16).
@@ -676,6 +772,8 @@ def dispatch_mlp_swiglu_combine_fwd_mxfp8(
               gate_shared=gate_shared, up_shared=up_shared, hidden_shared=hidden_shared, y_shared=y_shared, y_routed=y_routed,
               x_fp8=x_q, x_sc=x_sc, x_fp8_t=x_t, x_sc_t=x_t_sc, gate_fp8=gate_q, gate_sc=gate_sc, up_fp8=up_q, up_sc=up_sc,
               hidden_fp8=hid_q, hidden_sc=hid_sc, hidden_fp8_t=hid_t, hidden_sc_t=hid_t_sc, **scratch)
+    _staging = _attach_dedup(a, x, cap, ('x',), True, dedup_row_source, dedup_unique_peer, dedup_unique_token,
+                             dedup_unique_before)  # noqa: F841  (keeps the staging buffers alive until the launch is queued)
     check(lib().mok_moe_forward_mxfp8(_native.ctypes.byref(a), stream_ptr(x.device)), "dispatch_mlp_swiglu_combine_fwd_mxfp8")
     return (x_t, x_t_sc, gate_shared, gate_q, gate_sc, up_shared, up_q, up_sc, hidden_shared, hid_t, hid_t_sc, y_shared, y_routed)
 
@@ -699,6 +797,10 @@ def recompute_forward_context_mxfp8(
     num_comm_sms: int,
     macrobatch_size: int,
     minibatch_size: int,
+    dedup_row_source: torch.Tensor | None = None,
+    dedup_unique_peer: torch.Tensor | None = None,
+    dedup_unique_token: torch.Tensor | None = None,
+    dedup_unique_before: torch.Tensor | None = None,
 ) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor,
            torch.Tensor, torch.Tensor, torch.Tensor]:
     """MXFP8 context recomputation (first macrobatch): dispatch, quantize, gate / up GEMMs, SwiGLU, quantize.
@@ -739,6 +841,8 @@ def recompute_forward_context_mxfp8(
               gate_shared=gate_shared, up_shared=up_shared, hidden_shared=hidden_shared,
               x_fp8=x_q, x_sc=x_sc, x_fp8_t=x_t, x_sc_t=x_t_sc, gate_fp8=gate_q, gate_sc=gate_sc, up_fp8=up_q, up_sc=up_sc,
               hidden_fp8=hid_q, hidden_sc=hid_sc, hidden_fp8_t=hid_t, hidden_sc_t=hid_t_sc, **scratch)
+    _staging = _attach_dedup(a, x, cap, ('x',), True, dedup_row_source, dedup_unique_peer, dedup_unique_token,
+                             dedup_unique_before)  # noqa: F841  (keeps the staging buffers alive until the launch is queued)
     check(lib().mok_moe_recompute_mxfp8(_native.ctypes.byref(a), stream_ptr(x.device)), "recompute_forward_context_mxfp8")
     return (x_t, x_t_sc, gate_shared, gate_q, gate_sc, up_shared, up_q, up_sc, hidden_shared, hid_t, hid_t_sc)
 
@@ -792,6 +896,10 @@ def dispatch_mlp_swiglu_combine_bwd_mxfp8(
     num_comm_sms: int,
     macrobatch_size: int,
     minibatch_size: int,
+    dedup_row_source: torch.Tensor | None = None,
+    dedup_unique_peer: torch.Tensor | None = None,
+    dedup_unique_token: torch.Tensor | None = None,
+    dedup_unique_before: torch.Tensor | None = None,
 ) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor,
            torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor,
            torch.Tensor, torch.Tensor]:
@@ -872,6 +980,8 @@ def dispatch_mlp_swiglu_combine_bwd_mxfp8(
               d_w_shared_gate=d_w_shared_gate, d_w_shared_up=d_w_shared_up, d_w_shared_down=d_w_shared_down,
               d_w_routed_gate=d_w_routed_gate, d_w_routed_up=d_w_routed_up, d_w_routed_down=d_w_routed_down,
               row_scratch=row_scratch, **scratch)
+    _staging = _attach_dedup(a, x, cap, ('x', 'd_y'), macrobatch_size < cap, dedup_row_source, dedup_unique_peer, dedup_unique_token,
+                             dedup_unique_before)  # noqa: F841  (keeps the staging buffers alive until the launch is queued)
     check(lib().mok_moe_backward_mxfp8(_native.ctypes.byref(a), stream_ptr(dev)), "dispatch_mlp_swiglu_combine_bwd_mxfp8")
     return (d_x_shared, d_x_routed, d_gate_shared, d_gate_q, d_gate_sc, d_up_shared, d_up_q, d_up_sc, d_hidden_shared,
             d_hidden_routed, d_y_q, d_y_sc, d_w_shared_gate, d_w_routed_gate, d_w_shared_up, d_w_routed_up, d_w_shared_down,

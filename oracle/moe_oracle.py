@@ -89,6 +89,30 @@ def schedule_oracle(topk_all: np.ndarray, num_local_experts: int, schedule_capac
     return peer_rank, peer_token, np.array([base], dtype=np.int32), per_expert
 
 
+def dedup_oracle(peer_rank: np.ndarray, peer_token_idx: np.ndarray, topk: int, num_local_tokens: int):
+    """Index arrays of the de-duplicated dispatch for a finished schedule (integer, bit-exact).
+
+    The reference has no counterpart: its dispatch pulls one row per route (csrc/megakernel/dispatch_combine.cuh:74-77).
+    Definition: the distinct (source rank, token) pairs among the non-padding rows are numbered 0, 1, ... in the order
+    of their first row.  Returns (row_source[cap] = number of the row's pair, -1 on padding rows; unique_peer[U];
+    unique_token[U]; unique_before[cap/256 + 1] = pairs whose first row lies below row 256*i; U)."""
+    peer_rank = np.asarray(peer_rank)
+    cap = peer_rank.shape[0]
+    valid = np.nonzero(peer_rank >= 0)[0]
+    keys = peer_rank[valid].astype(np.int64) * num_local_tokens + np.asarray(peer_token_idx)[valid] // topk
+    uniq, first_pos, inverse = np.unique(keys, return_index=True, return_inverse=True)
+    order = np.argsort(first_pos, kind="stable")            # unique keys by first row
+    number_of = np.empty(len(uniq), dtype=np.int64)
+    number_of[order] = np.arange(len(uniq))
+    row_source = np.full(cap, -1, dtype=np.int32)
+    row_source[valid] = number_of[inverse].astype(np.int32)
+    unique_peer = (uniq[order] // num_local_tokens).astype(np.int32)
+    unique_token = (uniq[order] % num_local_tokens).astype(np.int32)
+    first_rows = np.sort(valid[first_pos])
+    unique_before = np.searchsorted(first_rows, np.arange(0, cap + 1, 256), side="left").astype(np.int32)
+    return row_source, unique_peer, unique_token, unique_before, len(uniq)
+
+
 # --------------------------------------------------------------------------------------------
 # MXFP8 quantizer (bytes are bit-exact)
 # --------------------------------------------------------------------------------------------

@@ -67,6 +67,18 @@ def check_group(group, dev, cases, seed: int, tag: str) -> None:
         assert torch.equal(out, out2), "output not bitwise reproducible"
         for name, a, b in zip(FIELDS, grads, grads2):
             assert torch.equal(a, b), f"{name} not bitwise reproducible"
+        # de-duplicated dispatch (the default for EP > 1: a token crosses NVLink once per destination rank) against the
+        # row-by-row pulls: the rows are copies either way, so everything downstream is bitwise equal
+        assert sched.row_source is not None and int(sched.num_unique.item()) <= int((sched.peer_rank >= 0).sum().item())
+        os.environ["MOK_NO_DEDUP"] = "1"
+        try:
+            sched3, out3, grads3 = once()
+        finally:
+            del os.environ["MOK_NO_DEDUP"]
+        assert sched3.row_source is None
+        assert torch.equal(out, out3), "output differs between de-duplicated and row-by-row dispatch"
+        for name, a, b in zip(FIELDS, grads, grads3):
+            assert torch.equal(a, b), f"{name} differs between de-duplicated and row-by-row dispatch"
 
         # the same layer in MXFP8 against the oracle that quantizes at the same points (rel-L2 <= 3e-2)
         emu = O.moe_layer_oracle(inputs, swiglu_limit=limit, mxfp8=True)[rank]

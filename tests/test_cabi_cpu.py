@@ -31,6 +31,11 @@ def test_entry_points_reject_bad_arguments_without_a_gpu():
     assert L.mok_fwd_epilogue(None, None, None, None, 512, 256, 1, None, None) == -1
     assert L.mok_bwd_epilogue(None, None, None, 512, 256, 1, None, None) == -1
     assert L.mok_barrier_all(None, None, 2, None, None, 0, None) == -1
+    assert L.mok_schedule_dedup(None, 2, 512, 2, 4, 2048, 0, None, None, None, None, None, None, None, None, 1024, None, None) == -1
+    assert L.mok_schedule_dedup_scratch_bytes(8, 32768, 8, 1048576) == 4 * (8 * 262144 + 1048576 + 4096)
+    assert L.mok_stage_unique_rows(None, 2, 0, None, None, None, None, 0, 256, 512, 256, None, 0, 0, None, None) == -1
+    assert L.mok_dispatch_rows_staged(None, None, 2, 0, None, None, None, None, None, 0, 0, 256, 2, 512, 256, None, None, 0, None,
+                                      None) == -1
     assert L.mok_grouped_gemm_bf16(None, None, None, None, None, 1, 256, 256, 64, 0, None, None) == -1
     args = nat.LayerArgs()
     assert L.mok_moe_forward_bf16(nat.ctypes.byref(args), None) == -1
@@ -95,6 +100,8 @@ def test_fake_impls_give_the_documented_shapes():
         q, sc, qt, sct = torch.ops.mok.mxfp8_quantize(x, True, True)
         assert q.shape == (3, 256, 384) and sc.shape == (6, 3, 32, 16) and qt.shape == (3, 384, 256) and sct.shape == (9, 2, 32, 16)
         assert q.dtype == torch.float8_e4m3fn and sc.dtype == torch.uint8
+        rs, up, ut, ub, nu = torch.ops.mok.schedule_dedup(topk_all, pr, pt, nt, 8, 1)
+        assert rs.shape == (4096,) and up.shape == ut.shape == (1024,) and ub.shape == (17,) and nu.shape == (1,)
 
 
 def _gloo_rank(rank, world, port, out):

@@ -27,7 +27,7 @@ static int rnd(int n) {
     } while (0)
 
 template <int BK>
-static int run_case(int case_index, int num_experts, int window_rows, bool trim) {
+static int run_case(int case_index, int num_experts, int window_rows, bool trim, int m_blocks, int n_blocks) {
     std::vector<int> tokens(num_experts), occupied(num_experts), cum(num_experts + 1, 0);
     for (int e = 0; e < num_experts; ++e) {
         const int valid = rnd(4) == 0 ? 0 : 1 + rnd(900);
@@ -41,8 +41,8 @@ static int run_case(int case_index, int num_experts, int window_rows, bool trim)
     p.tokens_per_expert = tokens.data();
     p.num_experts = num_experts;
     p.occupied_rows = trim ? occupied.data() : nullptr;
-    p.n_blocks = 3;
-    p.m_blocks_w = 2;
+    p.n_blocks = n_blocks;
+    p.m_blocks_w = m_blocks;
     p.k_blocks = 5;
     p.n_sets = 2;
     p.k_sets = 1;
@@ -68,11 +68,14 @@ static int run_case(int case_index, int num_experts, int window_rows, bool trim)
         }
         const int n_wgrad = total_tiles<MODE_WGRAD>(p, lo, hi);
         CHECK(n_wgrad == num_experts * p.m_blocks_w * p.n_blocks);
+        std::set<long long> wgrad_seen;                         // (expert, m tile, n tile) exactly once per window
         for (int t = 0; t < n_wgrad; ++t) {
             Tile tile;
             const bool work = decode_tile<MODE_WGRAD, BK>(p, cum.data(), lo, hi, t, tile);
             const int e = tile.expert;
             CHECK(e == t / (p.m_blocks_w * p.n_blocks));
+            CHECK(tile.m0 % BM == 0 && tile.m0 / BM < p.m_blocks_w && tile.n0 % BN == 0 && tile.n0 / BN < p.n_blocks);
+            CHECK(wgrad_seen.insert((static_cast<long long>(e) * 1024 + tile.m0 / BM) * 1024 + tile.n0 / BN).second);
             if (!work) continue;
             CHECK(tile.k_blocks > 0 && tile.row0 >= lo && tile.row0 + tile.k_blocks * BK <= hi);
             CHECK(tile.row0 >= cum[e] && tile.row0 + tile.k_blocks * BK <= cum[e + 1]);
@@ -103,10 +106,14 @@ int main() {
     for (int experts : {1, 3, 17, 64}) {
         for (int window : {256, 1024, 4096, 1 << 20}) {
             for (int trim = 0; trim < 2; ++trim) {
-                if (run_case<64>(case_index++, experts, window, trim != 0)) return 1;    // bf16 kernel's K step
-                if (run_case<128>(case_index++, experts, window, trim != 0)) return 1;   // MXFP8 kernel's K step
+                if (run_case<64>(case_index++, experts, window, trim != 0, 2, 3)) return 1;    // bf16 kernel's K step
+                if (run_case<128>(case_index++, experts, window, trim != 0, 2, 3)) return 1;   // MXFP8 kernel's K step
             }
         }
+        // output tile grids of the weight-gradient form: the benchmark's (8 x 28 and 28 x 8), square, one wide enough to
+        // be cut into groups with a narrower last group, and single-tile edges
+        for (auto mn : {std::pair<int, int>{8, 28}, {28, 8}, {13, 13}, {21, 30}, {1, 5}, {7, 1}})
+            if (run_case<64>(case_index++, experts, 4096, true, mn.first, mn.second)) return 1;
     }
     std::printf("ok %d cases\n", case_index);
     return 0;
