@@ -67,18 +67,22 @@ def check_group(group, dev, cases, seed: int, tag: str) -> None:
         assert torch.equal(out, out2), "output not bitwise reproducible"
         for name, a, b in zip(FIELDS, grads, grads2):
             assert torch.equal(a, b), f"{name} not bitwise reproducible"
-        # de-duplicated dispatch (the default for EP > 1: a token crosses NVLink once per destination rank) against the
-        # row-by-row pulls: the rows are copies either way, so everything downstream is bitwise equal
-        assert sched.row_source is not None and int(sched.num_unique.item()) <= int((sched.peer_rank >= 0).sum().item())
-        os.environ["MOK_NO_DEDUP"] = "1"
-        try:
-            sched3, out3, grads3 = once()
-        finally:
-            del os.environ["MOK_NO_DEDUP"]
-        assert sched3.row_source is None
-        assert torch.equal(out, out3), "output differs between de-duplicated and row-by-row dispatch"
-        for name, a, b in zip(FIELDS, grads, grads3):
-            assert torch.equal(a, b), f"{name} differs between de-duplicated and row-by-row dispatch"
+        # de-duplicated dispatch (a token crosses NVLink once per destination rank and is fanned out locally) against
+        # row-by-row pulls, each forced in turn: the rows are copies either way, so everything downstream is bitwise equal
+        variants = {}
+        for flag in ("1", "0"):
+            os.environ["MOK_DEDUP"] = flag
+            try:
+                variants[flag] = once()
+            finally:
+                del os.environ["MOK_DEDUP"]
+        staged, plain = variants["1"], variants["0"]
+        assert plain[0].row_source is None and staged[0].row_source is not None
+        assert int(staged[0].num_unique.item()) <= int((staged[0].peer_rank >= 0).sum().item())
+        for other in (staged, plain):
+            assert torch.equal(out, other[1]), "output differs between de-duplicated and row-by-row dispatch"
+            for name, a, b in zip(FIELDS, grads, other[2]):
+                assert torch.equal(a, b), f"{name} differs between de-duplicated and row-by-row dispatch"
 
         # the same layer in MXFP8 against the oracle that quantizes at the same points (rel-L2 <= 3e-2)
         emu = O.moe_layer_oracle(inputs, swiglu_limit=limit, mxfp8=True)[rank]
@@ -125,6 +129,9 @@ def run(rank: int, world: int, port: int) -> None:
     os.environ["MASTER_PORT"] = str(port)
     dev = torch.device("cuda", rank)
     torch.cuda.set_device(dev)
+    # every rank computes the CPU oracle of the whole group: share the host cores instead of oversubscribing them
+    # (eight processes with a full-size thread pool each spent a quarter of an hour here; one thread needs seconds)
+    torch.set_num_threads(max(1, len(os.sched_getaffinity(0)) // world))
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
     try:
         check_barrier_counters(dev)
