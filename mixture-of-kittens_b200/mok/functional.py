@@ -179,8 +179,13 @@ def create_workspace(config: MoKConfig, group: dist.ProcessGroup, *, device: tor
 
     symm_mem = None
     if ep_size > 1:
+        import warnings
         import torch.distributed._symmetric_memory as symm_mem
-        symm_mem.enable_symm_mem_for_group(group_name)
+        enable = getattr(symm_mem, "enable_symm_mem_for_group", None)   # newer PyTorch enables groups on first use
+        if enable is not None:
+            with warnings.catch_warnings():
+                warnings.simplefilter("ignore", FutureWarning)
+                enable(group_name)
     schedule_capacity = num_local_tokens * topk * _capacity_factor(config, ep_size)
 
     def allocate(*shape: int, dtype: torch.dtype, zero: bool = False):
