@@ -3,6 +3,7 @@
 // weight-gradient form, taken over all windows, cover each expert's occupied rows exactly once, in order, and the
 // "accumulate" flag is set exactly for the windows that do not hold the expert's first row.
 // Built and run by tests/test_tile_math_cpu.py (nvcc, host code only; no GPU needed).
+#include <algorithm>
 #include <cstdio>
 #include <cstdlib>
 #include <set>
@@ -101,8 +102,45 @@ static int run_case(int case_index, int num_experts, int window_rows, bool trim,
     return 0;
 }
 
+// The point of the weight-gradient tile order: the tiles that run at one time (one per CTA pair, 74 on a B200) should
+// share few operand panels.  For every run of 74 consecutive tiles inside one expert, count the distinct row panels
+// (m tiles, operand A) and column panels (n tiles, operand B) they touch.
+static int worst_panels_in_flight(int m_blocks, int n_blocks, int in_flight) {
+    std::vector<int> tokens(1, 1024), cum = {0, 1024};
+    KernelParams p{};
+    p.tokens_per_expert = tokens.data();
+    p.num_experts = 1;
+    p.m_blocks_w = m_blocks;
+    p.n_blocks = n_blocks;
+    p.row_begin = 0;
+    p.row_end = 1024;
+    const int total = m_blocks * n_blocks;
+    std::vector<std::pair<int, int>> order(total);
+    for (int t = 0; t < total; ++t) {
+        Tile tile;
+        decode_tile<MODE_WGRAD, 64>(p, cum.data(), 0, 1024, t, tile);
+        order[t] = {tile.m0 / BM, tile.n0 / BN};
+    }
+    int worst = 0;
+    for (int start = 0; start + in_flight <= total; ++start) {
+        std::set<int> ms, ns;
+        for (int t = start; t < start + in_flight; ++t) {
+            ms.insert(order[t].first);
+            ns.insert(order[t].second);
+        }
+        worst = std::max(worst, static_cast<int>(ms.size() + ns.size()));
+    }
+    return worst;
+}
+
 int main() {
     int case_index = 0;
+    // the layer's two weight-gradient grids (2048 x 7168 and 7168 x 2048 outputs): at most 8 + 11 panels in flight,
+    // where a plain row-major walk of the 8 x 28 grid touches 4 + 28
+    if (worst_panels_in_flight(8, 28, 74) > 19 || worst_panels_in_flight(28, 8, 74) > 19) {
+        std::printf("FAILED panels in flight: %d %d\n", worst_panels_in_flight(8, 28, 74), worst_panels_in_flight(28, 8, 74));
+        return 1;
+    }
     for (int experts : {1, 3, 17, 64}) {
         for (int window : {256, 1024, 4096, 1 << 20}) {
             for (int trim = 0; trim < 2; ++trim) {
